@@ -28,7 +28,8 @@ class StackLayer(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("mixer", "heads", "kv_heads", "dim", "vdim", "rot_dims", "rot_table", "vrot_table")] + \
                [("scale", C.c_float)] + [(n, C.c_int32) for n in ("mlp", "experts", "top", "groups", "keep", "ff")] + \
                [(n, C.c_int32) for n in ("kv_rank", "rot_dim", "mixer_flags")] + [("gate_cap", C.c_float)] + \
-               [(n, C.c_int32) for n in ("act", "ungated", "sigmoid_scores", "weight_input", "shared_ff")]
+               [(n, C.c_int32) for n in ("act", "ungated", "sigmoid_scores", "weight_input", "shared_ff")] + \
+               [(n, C.c_int32) for n in ("window", "q_rank", "kv_share", "conv_taps", "decay_rank", "gate_rank")]
 
 
 class StackCfg(C.Structure):
@@ -36,20 +37,23 @@ class StackCfg(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("width", "vocab", "n_layers")] + [("embed_scale", C.c_float), ("norm_eps", C.c_float)] + \
                [(n, C.c_int32) for n in ("f32", "block_size", "max_tokens", "max_blocks_per_seq", "max_logit_rows")] + \
                [(n, C.c_int32) for n in ("form", "canon_taps", "depth_avg", "bigram_buckets", "bigram_mul_prev", "bigram_mul_cur")] + \
-               [("logit_softcap", C.c_float), ("n_state_slots", C.c_int32)]
+               [("logit_softcap", C.c_float), ("n_state_slots", C.c_int32), ("residual_alpha", C.c_float)]
 
 
-MIXER_ATTENTION, MIXER_LATENT, MIXER_MLSTM = 1, 2, 3
+MIXER_ATTENTION, MIXER_LATENT, MIXER_MLSTM, MIXER_DELTA = 1, 2, 3, 4
 MLP_NONE, MLP_MOE, MLP_DENSE = 0, 1, 2
-ACT_SILU, ACT_GELU_TANH, ACT_RELU2 = 0, 1, 2
-ACTS = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH, "relu2": ACT_RELU2}
-FORM_SANDWICH, FORM_PARALLEL = 0, 1
-MIXF_SINK, MIXF_GATE = 1, 2
+ACT_SILU, ACT_GELU_TANH, ACT_RELU2, ACT_RELU = 0, 1, 2, 3
+ACTS = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH, "relu2": ACT_RELU2, "relu": ACT_RELU}
+FORM_SANDWICH, FORM_PARALLEL, FORM_POSTNORM = 0, 1, 2
+MIXF_SINK, MIXF_GATE, MIXF_HEAD_NORM, MIXF_VALUE_IS_KEY, MIXF_SINK_ONE, MIXF_HEAD_GATE = 1, 2, 4, 8, 16, 32
 (SW_EMBED, SW_FINAL_NORM, SW_HEAD, SW_NORM_MIX_PRE, SW_NORM_MIX_POST, SW_NORM_MLP_PRE, SW_NORM_MLP_POST, SW_QKV, SW_Q_NORM,
  SW_K_NORM, SW_O, SW_ROUTER, SW_ROUTER_BIAS, SW_EXPERT_GATE_UP, SW_EXPERT_DOWN, SW_BIGRAM, SW_CANON, SW_DEPTH_AVG, SW_UK_T, SW_UV,
- SW_SINK, SW_GATES, SW_GATES_BIAS, SW_HEAD_NORM, SW_MLP_GATE_UP, SW_MLP_DOWN, SW_SHARED_UP, SW_SHARED_DOWN) = range(28)
+ SW_SINK, SW_GATES, SW_GATES_BIAS, SW_HEAD_NORM, SW_MLP_GATE_UP, SW_MLP_DOWN, SW_SHARED_UP, SW_SHARED_DOWN, SW_NORM_MIX_POST_BIAS,
+ SW_NORM_MLP_POST_BIAS, SW_FINAL_NORM_BIAS, SW_Q_LATENT_NORM, SW_UQ, SW_CONV, SW_DECAY_UP, SW_DECAY_BIAS, SW_DECAY_LOG,
+ SW_GATE_UP) = range(38)
 SW_F32 = {SW_FINAL_NORM, SW_NORM_MIX_PRE, SW_NORM_MIX_POST, SW_NORM_MLP_PRE, SW_NORM_MLP_POST, SW_Q_NORM, SW_K_NORM, SW_ROUTER_BIAS,
-          SW_CANON, SW_DEPTH_AVG, SW_SINK, SW_GATES_BIAS, SW_HEAD_NORM}
+          SW_CANON, SW_DEPTH_AVG, SW_SINK, SW_GATES_BIAS, SW_HEAD_NORM, SW_NORM_MIX_POST_BIAS, SW_NORM_MLP_POST_BIAS,
+          SW_FINAL_NORM_BIAS, SW_Q_LATENT_NORM, SW_CONV, SW_DECAY_BIAS, SW_DECAY_LOG}
 
 W_EMBED, W_LN1, W_QKV, W_QKV_BIAS, W_O, W_LN2, W_GATE_UP, W_DOWN, W_FINAL_NORM, W_LM_HEAD, W_GATE_UP_INTERLEAVED = range(11)
 
@@ -148,6 +152,19 @@ SIGNATURES = {
     "b200_head_norm_gate": (C.c_int, [_i32, _vp, _vp, _vp, _i64, _vp, _i32, _i32, _i32, _f32, _vp]),
     "b200_ff_act": (C.c_int, [_i32, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
     "b200_moe_route_scores": (C.c_int, [_i32, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),
+    "b200_delta_fused_rows": (_i32, [_i32, _i32, _i32, _i32, _i32, _i32, _vp]),
+    "b200_postnorm_stream": (C.c_int, [_i32, _vp, _vp, _f32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _f32, _vp]),
+    "b200_qk_headnorm_rotate_cache": (C.c_int, [_i32, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _vp, _vp, _vp, _i32, _i32, _i32, _i32,
+                                                _i32, _i32, _f32, _vp]),
+    "b200_paged_attn_window": (C.c_int, [_i32, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _f32,
+                                         _i32, _vp, _i32, _i32, _vp, _i32, _vp]),
+    "b200_latent_attn_window": (C.c_int, [_vp, _vp, _vp, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _f32, _vp, _vp, _i32, _vp]),
+    "b200_latent_norms": (C.c_int, [_i32, _vp, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _f32, _vp]),
+    "b200_head_linear_head_gate": (C.c_int, [_i32, _vp, _i64, _i32, _vp, _vp, _i64, _i32, _vp, _i64, _i32, _i32, _i32, _i32, _vp]),
+    "b200_delta_prep": (C.c_int, [_i32, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _i32, _i32,
+                                  _i32, _i32, _i32, _i32, _i32, _i32, _vp]),
+    "b200_delta_tails": (C.c_int, [_i32, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _vp]),
+    "b200_delta_scan": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _i32, _i32, _i32, _i32, _i32, _vp]),
     "b200_moe_experts_form": (C.c_int, [_i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _i32, _i32, _i32, _vp]),
 }
 

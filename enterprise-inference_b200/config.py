@@ -145,7 +145,9 @@ class RotarySpec:
     """Rotation of the leading `dims` dimensions of a head in the interleaved pair layout (2i, 2i+1), pair i turning by
     position * f_i with f_i = base^(-2i/dims).  With YaRN scaling (factor, original, fast, slow) the frequencies are
     blended between f_i and f_i / factor by a linear ramp over the pair index and cos/sin are multiplied by
-    0.1 ln(factor) + 1."""
+    0.1 ln(factor) + 1.  kind "bands" scales by wavelength instead: with l = 2 pi / f_i, pairs with l < original / fast keep
+    f_i, pairs with l > original / slow get f_i / factor, and those between are blended linearly in original / l; cos/sin keep
+    their magnitude."""
     base: float
     dims: int
     factor: float = 1.0
@@ -153,9 +155,10 @@ class RotarySpec:
     fast: float = 0.0
     slow: float = 0.0
     scaled: bool = False
+    kind: str = "yarn"
 
     def key(self) -> tuple:
-        return (self.base, self.dims, self.factor, self.original, self.fast, self.slow, self.scaled)
+        return (self.base, self.dims, self.factor, self.original, self.fast, self.slow, self.scaled, self.kind)
 
     def frequencies(self) -> Tuple[torch.Tensor, float]:
         """(f[dims/2] float64, magnitude factor)."""
@@ -163,6 +166,12 @@ class RotarySpec:
         f = torch.tensor(self.base, dtype=torch.float64) ** (-2.0 * i / self.dims)
         if not self.scaled:
             return f, 1.0
+        if self.kind == "bands":
+            lam = 2.0 * math.pi / f
+            blend = (self.original / lam - self.slow) / (self.fast - self.slow)
+            mid = (1.0 - blend) * f / self.factor + blend * f
+            out = torch.where(lam < self.original / self.fast, f, torch.where(lam > self.original / self.slow, f / self.factor, mid))
+            return out, 1.0
 
         def pair_of(turns: float) -> float:   # the (fractional) pair index whose wavelength makes `turns` turns over `original` positions
             return self.dims * math.log(self.original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.base))
@@ -188,6 +197,10 @@ class AttentionSpec:
     scale: float
     rot: Optional[RotarySpec] = None       # q/k rotation (None: none)
     value_rot: Optional[RotarySpec] = None  # values rotate by their position, outputs turn back by the query's (None: off)
+    window: int = 0                        # positions a query sees, its own included (0: all)
+    head_norm: bool = False                # q/k RMS norm per head with one weight of `dim` entries (else over the whole projection)
+    value_is_key: bool = False             # no value projection: a value is the key projection before norm and rotation
+    sink_one: bool = False                 # one more unit in the softmax denominator
 
 
 @dataclass
@@ -201,8 +214,8 @@ class MoESpec:
 
 @dataclass
 class StackLayerSpec:
-    mixer: AttentionSpec
-    mlp: Optional[MoESpec] = None
+    mixer: object                     # AttentionSpec | LatentAttentionSpec | ChannelDeltaSpec
+    mlp: Optional[object] = None      # MoESpec | FeedForwardSpec
 
 
 @dataclass
@@ -302,6 +315,10 @@ class LatentAttentionSpec:
     sink: bool = False
     gate: bool = False
     kind: str = "latent"
+    q_rank: int = 0                        # > 0: queries pass a normed latent of this size
+    window: int = 0                        # positions a query sees, its own included (0: all)
+    head_gate: bool = False                # one sigmoid gate per head (instead of one per output)
+    kv_from: Optional[int] = None          # the layer whose cached latent rows this layer reads (None: its own)
 
 
 @dataclass
@@ -431,8 +448,163 @@ class DupolornConfig:
                               bigram_mul_cur=int(bg.get("mul_cur", 0)), logit_softcap=float(c.get("logit_softcap") or 0.0), layers=layers)
 
 
+# ---- Futidra ----------------------------------------------------------------------------------------------------------------
+@dataclass
+class ChannelDeltaSpec:
+    """Delta-rule recurrence with one decay per head and key channel: q/k in `kv_heads` heads of `dim`, values in `heads` heads of
+    `vdim`, a causal convolution of `conv` taps on q, k and v, two-step projections of inner sizes `decay_rank` / `gate_rank` for
+    the decays and the output gate."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    conv: int
+    decay_rank: int
+    gate_rank: int
+    kind: str = "delta"
+
+
+@dataclass
+class FutidraConfig:
+    """Futidra: decoder-only, norm after the sum: x = LN(alpha x + mixer(x)), x = LN(alpha x + ff(x)) with layer norms that have
+    weight and bias.  Mixers: windowed grouped-query attention whose values are its keys (per-head q/k norms, partial pair
+    rotation with band-scaled frequencies, one more unit in the softmax denominator); windowed latent attention without positions
+    (query latent, per-head output gate, optionally reading another layer's cached latents); the channel-decay delta rule.
+    Dense relu-gated feed-forwards; the output projection is the embedding table."""
+    name: str = "futidra"
+    width: int = 256
+    vocab: int = 1024
+    norm_eps: float = 1e-6
+    postln_alpha: float = 1.0
+    layers: List[StackLayerSpec] = field(default_factory=list)
+    architecture: str = "Futidra"
+    embed_scale: float = 1.0
+
+    @property
+    def hidden(self) -> int:
+        return self.width
+
+    @property
+    def n_layers(self) -> int:
+        return len(self.layers)
+
+    @property
+    def needs_state(self) -> bool:
+        return any(isinstance(L.mixer, ChannelDeltaSpec) for L in self.layers)
+
+    def to_dict(self):
+        return asdict(self)
+
+    def _layer_params(self, L) -> int:
+        W, a = self.width, L.mixer
+        if isinstance(a, ChannelDeltaSpec):
+            n = W * (2 * a.kv_heads * a.dim + a.heads * a.vdim + a.heads + a.decay_rank + a.gate_rank)
+            n += a.heads * a.dim * a.decay_rank + a.heads * a.vdim * a.gate_rank + a.heads * a.vdim * W
+        elif isinstance(a, LatentAttentionSpec):
+            n = W * (a.q_rank + (0 if a.kv_from is not None else a.kv_rank) + a.heads) + a.heads * a.dim * a.q_rank
+            n += a.heads * a.kv_rank * (a.dim + a.vdim) + a.heads * a.vdim * W
+        else:
+            n = W * (a.heads + a.kv_heads) * a.dim + a.heads * a.vdim * W
+        if L.mlp is not None:
+            n += 3 * L.mlp.ff * W
+        return n
+
+    def decode_params(self) -> int:
+        return self.vocab * self.width + sum(self._layer_params(L) for L in self.layers)
+
+    def weight_bytes(self) -> int:
+        return 2 * self.decode_params()
+
+    def kv_bytes_per_token(self, f32: bool = False) -> int:
+        n = 0
+        for L in self.layers:
+            a = L.mixer
+            if isinstance(a, AttentionSpec):
+                n += a.kv_heads * (a.dim + a.vdim)
+            elif isinstance(a, LatentAttentionSpec) and a.kv_from is None:
+                n += a.kv_rank
+        return n * (4 if f32 else 2)
+
+    @staticmethod
+    def from_dict(c: dict, name: str = "futidra", shapes: Optional[Dict[str, list]] = None) -> "FutidraConfig":
+        """`shapes` (tensor name -> shape, from the checkpoint) gives the sizes config.json does not name: the inner sizes of the
+        delta mixer's two-step projections."""
+        layers = []
+        for i, l in enumerate(c["layers"]):
+            kind, m = l.get("type"), l["mixer"]
+            window = int((m.get("mask") or {}).get("size", 0))
+            if kind == "attention":
+                rot = None
+                r = m.get("rot")
+                if r and int(r["dims"]) > 0:
+                    sc = r.get("scaling") or None
+                    if sc:
+                        rot = RotarySpec(base=float(r["base"]), dims=int(r["dims"]), factor=float(sc["factor"]), original=int(sc["original"]),
+                                         fast=float(sc["high"]), slow=float(sc["low"]), scaled=True, kind="bands")
+                    else:
+                        rot = RotarySpec(base=float(r["base"]), dims=int(r["dims"]))
+                    if rot.dims % 2 or rot.dims > int(m["dim"]):
+                        raise ValueError(f"layer {i}: {rot.dims} rotated dimensions in heads of {m['dim']}")
+                mixer = AttentionSpec(heads=int(m["heads"]), kv_heads=int(m.get("kv_heads", m["heads"])), dim=int(m["dim"]),
+                                      vdim=int(m.get("vdim", m["dim"])), scale=float(m["scale"]), rot=rot, window=window, head_norm=True,
+                                      value_is_key=True, sink_one=True)
+                if mixer.vdim > mixer.dim:
+                    raise ValueError(f"layer {i}: values of {mixer.vdim} dimensions cannot be keys of {mixer.dim}")
+            elif kind == "latent_attention":
+                src = m.get("kv_from")
+                mixer = LatentAttentionSpec(heads=int(m["heads"]), dim=int(m["dim"]), rot_dim=0, vdim=int(m["vdim"]), kv_rank=int(m["kv_rank"]),
+                                            scale=float(m["scale"]), q_rank=int(m["q_rank"]), window=window, head_gate=True,
+                                            kv_from=None if src is None else int(src))
+                if mixer.kv_from is not None:
+                    j = mixer.kv_from
+                    if not (0 <= j < i) or not isinstance(layers[j].mixer, LatentAttentionSpec) or layers[j].mixer.kv_from is not None \
+                            or layers[j].mixer.kv_rank != mixer.kv_rank:
+                        raise ValueError(f"layer {i}: kv_from {j} is not an earlier latent layer with a latent of its own of size {mixer.kv_rank}")
+            elif kind == "channel_delta":
+                ranks = []
+                for key, tensor in (("decay_rank", f"l{i}.mix.a1"), ("gate_rank", f"l{i}.mix.g1")):
+                    if shapes is not None and tensor in shapes:
+                        ranks.append(int(shapes[tensor][0]))
+                    elif key in m:
+                        ranks.append(int(m[key]))
+                    else:
+                        raise ValueError(f"layer {i}: the size of {tensor} is needed (checkpoint shapes or mixer[{key!r}])")
+                mixer = ChannelDeltaSpec(heads=int(m["heads"]), kv_heads=int(m.get("kv_heads", m["heads"])), dim=int(m["dim"]), vdim=int(m["vdim"]),
+                                         conv=int(m.get("conv", 1)), decay_rank=ranks[0], gate_rank=ranks[1])
+                if mixer.heads % mixer.kv_heads:
+                    raise ValueError(f"layer {i}: {mixer.heads} heads over {mixer.kv_heads} q/k heads")
+            else:
+                raise ValueError(f"layer {i}: unsupported mixer type {kind!r} (this design has attention, latent_attention, channel_delta)")
+            mlp = None
+            f = l.get("mlp")
+            if f:
+                if f.get("kind", "dense") != "dense":
+                    raise ValueError(f"layer {i}: unsupported feed-forward kind {f.get('kind')!r}")
+                mlp = FeedForwardSpec(kind="dense", ff=int(f["ff"]), act="relu")
+            layers.append(StackLayerSpec(mixer=mixer, mlp=mlp))
+        return FutidraConfig(name=name, width=int(c["width"]), vocab=int(c["vocab"]), norm_eps=float((c.get("norm") or {}).get("eps", 1e-6)),
+                             postln_alpha=float(c.get("postln_alpha", 1.0)), layers=layers)
+
+
+def checkpoint_shapes(path: str) -> Dict[str, list]:
+    """Tensor name -> shape of every *.safetensors file under `path`, from the files' headers alone (8-byte little-endian
+    length, then that many bytes of JSON)."""
+    import glob
+    import struct
+    out: Dict[str, list] = {}
+    for fn in sorted(glob.glob(os.path.join(path, "*.safetensors"))):
+        with open(fn, "rb") as f:
+            (n,) = struct.unpack("<Q", f.read(8))
+            head = json.loads(f.read(n))
+        for k, v in head.items():
+            if k != "__metadata__":
+                out[k] = list(v["shape"])
+    return out
+
+
 # config.json "architecture" -> reader.  HF-style configs (model_type) go through from_hf_config.
-ARCHITECTURES = {"Bopilorn": BopilornConfig.from_dict, "Dupolorn": DupolornConfig.from_dict}
+ARCHITECTURES = {"Bopilorn": BopilornConfig.from_dict, "Dupolorn": DupolornConfig.from_dict, "Futidra": FutidraConfig.from_dict}
+NEEDS_SHAPES = {"Futidra"}   # readers that take the checkpoint's tensor shapes for sizes config.json does not name
 
 
 def load_model_config(path: str):
@@ -443,6 +615,8 @@ def load_model_config(path: str):
     if arch is not None:
         if arch not in ARCHITECTURES:
             raise ValueError(f"unsupported architecture {arch!r} (known: {sorted(ARCHITECTURES)})")
+        if arch in NEEDS_SHAPES:
+            return ARCHITECTURES[arch](c, name=c.get("_name_or_path", path), shapes=checkpoint_shapes(path))
         return ARCHITECTURES[arch](c, name=c.get("_name_or_path", path))
     return from_hf_config(path)
 

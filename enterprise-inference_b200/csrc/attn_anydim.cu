@@ -1,4 +1,5 @@
-// Paged causal softmax attention for heads of any size (query/key size `dim`, value size `vdim`, dim != vdim allowed),
+// Paged causal softmax attention (optionally over a sliding window of the last `window` keys) for heads of any size
+// (query/key size `dim`, value size `vdim`, dim != vdim allowed),
 // any block size, a caller-given score scale, fp32 queries and a bf16 or fp32 cache.  The tcgen05 kernels of attn_tc.cu /
 // attn_prefill.cu are built for 128-wide heads; this file serves every other head shape on CUDA cores with fp32 scores,
 // fp32 softmax weights and fp32 accumulation.
@@ -51,7 +52,7 @@ paged_attn_rows_kernel(const float* __restrict__ q, const CT* __restrict__ kc, c
                        const int32_t* __restrict__ block_table, int bt_stride, const int32_t* __restrict__ row_to_seq,
                        const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ positions,
                        const float* __restrict__ vrot, int64_t max_pos, AT* __restrict__ out, int heads, int kv_heads,
-                       int dim, int vdim, int block_size, float scale, int kst, int vst, const float* __restrict__ sink) {
+                       int dim, int vdim, int block_size, float scale, int kst, int vst, const float* __restrict__ sink, int window) {
   extern __shared__ float sm[];
   float* qs = sm;                 // [dim]
   float* ps = qs + dim;           // [128] weights of the tile
@@ -70,11 +71,12 @@ paged_attn_rows_kernel(const float* __restrict__ q, const CT* __restrict__ kc, c
 #pragma unroll
   for (int i = 0; i < kAdMaxVPer; ++i) acc[i] = 0.f;
   __syncthreads();
-  for (int base = 0; base < ctx; base += kAdThreads) {
+  const int lo = window > 0 ? max(ctx - window, 0) : 0;   // the first key the row sees; the tile that holds it is the first walked
+  for (int base = lo - lo % kAdThreads; base < ctx; base += kAdThreads) {
     const int j = base + tid;
     float sc = -INFINITY;
     int blk = 0;
-    if (j < ctx) {
+    if (j < ctx && j >= lo) {
       blk = bt[j / block_size];
       const CT* kp = kc + (((int64_t)blk * kv_heads + g) * block_size + j % block_size) * kst;
       float a = 0.f;
@@ -83,7 +85,7 @@ paged_attn_rows_kernel(const float* __restrict__ q, const CT* __restrict__ kc, c
     }
     const float tm = block_max128(sc, red);
     const float mn = fmaxf(m, tm);
-    const float p = j < ctx ? expf(sc - mn) : 0.f;
+    const float p = (j < ctx && j >= lo) ? expf(sc - mn) : 0.f;
     const float corr = expf(m - mn);      // first tile: exp(-inf) = 0
     const float ts = block_sum128(p, red);
     l = l * corr + ts;
@@ -97,7 +99,7 @@ paged_attn_rows_kernel(const float* __restrict__ q, const CT* __restrict__ kc, c
       const int d = tid + i * kAdThreads;
       if (d < vdim) {
         float a = acc[i] * corr;
-        for (int jj = 0; jj < n; ++jj) {
+        for (int jj = max(lo - base, 0); jj < n; ++jj) {
           const CT* vp = vc + (((int64_t)blk_of[jj] * kv_heads + g) * block_size + (base + jj) % block_size) * vst;
           a = fmaf(ps[jj], cache_load<CT>(vp, d), a);
         }
@@ -205,7 +207,7 @@ paged_attn_runs_kernel(const float* __restrict__ q, const CT* __restrict__ kc, c
                        const int32_t* __restrict__ ctx_lens, const int32_t* __restrict__ positions,
                        const float* __restrict__ vrot, int64_t max_pos, AT* __restrict__ out,
                        const int32_t* __restrict__ runs, const int32_t* __restrict__ n_runs, int heads, int kv_heads, int dim,
-                       int vdim, int block_size, float scale, int kcs, int vcs, const float* __restrict__ sink) {
+                       int vdim, int block_size, float scale, int kcs, int vcs, const float* __restrict__ sink, int window) {
   extern __shared__ float sm[];
   pdl_wait();
   pdl_launch_dependents();
@@ -237,7 +239,9 @@ paged_attn_runs_kernel(const float* __restrict__ q, const CT* __restrict__ kc, c
     l[k] = 0.f;
   }
   __syncthreads();
-  for (int base = 0; base < ctx_max; base += kTileKeys) {
+  // with a window the run's first row sees the oldest key of all: the walk starts at the tile that holds it
+  const int lo_run = window > 0 ? max(ctx_lens[t0] - window, 0) : 0;
+  for (int base = lo_run - lo_run % kTileKeys; base < ctx_max; base += kTileKeys) {
     const int n = min(kTileKeys, ctx_max - base);
     for (int i = threadIdx.x; i < n * dim; i += kTcThreads) {
       const int jj = i / dim, d = i % dim, j = base + jj;
@@ -254,10 +258,11 @@ paged_attn_runs_kernel(const float* __restrict__ q, const CT* __restrict__ kc, c
       if (qi < nq) {
         const int r = qi / G;
         const int ctx = ctx_lens[t0 + r];
-        if (base < ctx) {
+        const int lo = window > 0 ? max(ctx - window, 0) : 0;
+        if (base < ctx && base + n > lo) {
           const int j = base + lane;
           float sc = -INFINITY;
-          if (j < ctx) {
+          if (j < ctx && j >= lo) {
             const float* qp = Qs + qi * dim;
             const float* kp = Ks + lane * kst;
             float a = 0.f;
@@ -265,7 +270,7 @@ paged_attn_runs_kernel(const float* __restrict__ q, const CT* __restrict__ kc, c
             sc = a * scale;
           }
           const float mn = fmaxf(m[k], warp_max(sc));
-          const float p = j < ctx ? expf(sc - mn) : 0.f;
+          const float p = (j < ctx && j >= lo) ? expf(sc - mn) : 0.f;
           const float corr = expf(m[k] - mn);
           l[k] = l[k] * corr + warp_sum(p);
           m[k] = mn;
@@ -333,7 +338,7 @@ template <typename CT, typename AT>
 static int paged_attn_anydim_t(const float* q, const void* kc, const void* vc, const int32_t* block_table, int bt_stride,
                                const int32_t* row_to_seq, const int32_t* ctx_lens, const int32_t* positions, const float* vrot,
                                int64_t max_pos, void* out, int T, int heads, int kv_heads, int dim, int vdim, int block_size,
-                               float scale, int plan, void* ws, cudaStream_t s, int kst, int vst, const float* sink) {
+                               float scale, int plan, void* ws, cudaStream_t s, int kst, int vst, const float* sink, int window) {
   const int G = heads / kv_heads;
   const size_t smem_runs = ((size_t)kTileKeys * (dim + 1 + vdim) + (size_t)kRunRows * G * (dim + vdim)) * 4;
   if (plan != 0 && ws != nullptr && kRunRows * G <= 16 * (kTcThreads / 32) && smem_runs <= 200 * 1024) {
@@ -344,13 +349,13 @@ static int paged_attn_anydim_t(const float* q, const void* kc, const void* vc, c
     if (smem_runs > 48 * 1024) B200_CUDA(ensure_dynamic_smem(paged_attn_runs_kernel<CT, AT>, 200 * 1024, done));
     B200_CUDA(launch(paged_attn_runs_kernel<CT, AT>, dim3(T, kv_heads), dim3(kTcThreads), smem_runs, s, q, (const CT*)kc,
                      (const CT*)vc, block_table, bt_stride, row_to_seq, ctx_lens, positions, vrot, max_pos, (AT*)out,
-                     (const int32_t*)runs, (const int32_t*)n_runs, heads, kv_heads, dim, vdim, block_size, scale, kst, vst, sink));
+                     (const int32_t*)runs, (const int32_t*)n_runs, heads, kv_heads, dim, vdim, block_size, scale, kst, vst, sink, window));
     return B200_OK;
   }
   const size_t smem = ((size_t)dim + kAdThreads + vdim) * 4;
   B200_CUDA(launch(paged_attn_rows_kernel<CT, AT>, dim3(T, heads), dim3(kAdThreads), smem, s, q, (const CT*)kc, (const CT*)vc,
                    block_table, bt_stride, row_to_seq, ctx_lens, positions, vrot, max_pos, (AT*)out, heads, kv_heads, dim, vdim,
-                   block_size, scale, kst, vst, sink));
+                   block_size, scale, kst, vst, sink, window));
   return B200_OK;
 }
 
@@ -359,17 +364,17 @@ static int paged_attn_anydim_t(const float* q, const void* kc, const void* vc, c
 int paged_attn_anydim(bool f32, const float* q, const void* kc, const void* vc, const int32_t* block_table, int bt_stride,
                       const int32_t* row_to_seq, const int32_t* ctx_lens, const int32_t* positions, const float* vrot,
                       int64_t max_pos, void* out, int T, int heads, int kv_heads, int dim, int vdim, int block_size, float scale,
-                      int plan, void* ws, cudaStream_t s, int kstride, int vstride, const float* sink) {
+                      int plan, void* ws, cudaStream_t s, int kstride, int vstride, const float* sink, int window) {
   if (T == 0) return B200_OK;
   const int kst = kstride > 0 ? kstride : dim, vst = vstride > 0 ? vstride : vdim;
   B200_REQUIRE(kst >= dim && vst >= vdim, B200_ERR_INVALID, "attention: cache rows of %d / %d elements for heads of %d / %d", kst, vst, dim, vdim);
   B200_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0, B200_ERR_INVALID, "attention: %d heads over %d kv heads", heads, kv_heads);
   B200_REQUIRE(vdim <= kAdThreads * kAdMaxVPer && dim <= 8192, B200_ERR_UNSUPPORTED, "attention: head sizes %d / %d too large", dim, vdim);
   return f32 ? paged_attn_anydim_t<float, float>(q, kc, vc, block_table, bt_stride, row_to_seq, ctx_lens, positions, vrot, max_pos,
-                                                 out, T, heads, kv_heads, dim, vdim, block_size, scale, plan, ws, s, kst, vst, sink)
+                                                 out, T, heads, kv_heads, dim, vdim, block_size, scale, plan, ws, s, kst, vst, sink, window)
              : paged_attn_anydim_t<__nv_bfloat16, __nv_bfloat16>(q, kc, vc, block_table, bt_stride, row_to_seq, ctx_lens,
                                                                  positions, vrot, max_pos, out, T, heads, kv_heads, dim, vdim,
-                                                                 block_size, scale, plan, ws, s, kst, vst, sink);
+                                                                 block_size, scale, plan, ws, s, kst, vst, sink, window);
 }
 
 }  // namespace b200

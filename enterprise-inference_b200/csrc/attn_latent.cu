@@ -1,4 +1,5 @@
-// Paged causal attention over latent cache rows on the tensor cores (bf16 serving mode of B200_MIXER_LATENT).
+// Paged causal attention over latent cache rows on the tensor cores (bf16 serving mode of B200_MIXER_LATENT), over the whole
+// context or over a sliding window of its last `window` keys.
 //
 // One kv head serves every query head, and a key row's leading `rank` entries are its value, so all heads of a token share
 // every byte of the cache: a CTA takes 16 (row, head) pairs of one run of consecutive rows of a sequence and walks the
@@ -53,7 +54,7 @@ latent_attn_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __restr
                        int bt_stride, const int32_t* __restrict__ row_to_seq, const int32_t* __restrict__ ctx_lens,
                        __nv_bfloat16* __restrict__ out, const int32_t* __restrict__ runs, const int32_t* __restrict__ n_runs, int heads,
                        int krow, int rank, int block_size, float scale, const float* __restrict__ sink, int n_splits,
-                       float* __restrict__ part) {
+                       float* __restrict__ part, int window) {
   extern __shared__ __align__(16) unsigned char smraw[];
   pdl_wait();
   pdl_launch_dependents();
@@ -71,10 +72,12 @@ latent_attn_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __restr
   float* mrow = corr + kLaPairs;
   float* lrow = mrow + kLaPairs;
   int* ctxp = reinterpret_cast<int*>(lrow + kLaPairs);
+  int* lop = ctxp + kLaPairs;   // the first key a pair sees (0 without a window)
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid < kLaPairs) {
     const int i = i0 + tid;
     ctxp[tid] = i < nq ? ctx_lens[t0 + i / heads] : 0;
+    lop[tid] = window > 0 ? max(ctxp[tid] - window, 0) : 0;
     mrow[tid] = -INFINITY;
     lrow[tid] = 0.f;
   }
@@ -94,8 +97,10 @@ latent_attn_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __restr
   __syncthreads();
 
   // with n_splits > 1 this CTA walks only its share of the tiles and leaves unnormalised sums for the merge kernel
-  const int tiles = (ctx_max + kLaKeys - 1) / kLaKeys, per = (tiles + n_splits - 1) / n_splits;
-  const int base_lo = blockIdx.z * per * kLaKeys, base_hi = min(ctx_max, (int)(blockIdx.z + 1) * per * kLaKeys);
+  // (with a window the walk starts at the tile that holds the oldest key the group's first row sees)
+  const int tile0 = window > 0 ? max(ctx_lens[t0 + i0 / heads] - window, 0) / kLaKeys : 0;
+  const int tiles = (ctx_max + kLaKeys - 1) / kLaKeys - tile0, per = (tiles + n_splits - 1) / n_splits;
+  const int base_lo = (tile0 + blockIdx.z * per) * kLaKeys, base_hi = min(ctx_max, (tile0 + (int)(blockIdx.z + 1) * per) * kLaKeys);
   for (int base = base_lo; base < base_hi; base += kLaKeys) {
     const int n = min(kLaKeys, ctx_max - base);
     {
@@ -135,16 +140,17 @@ latent_attn_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __restr
     // softmax bookkeeping: this warp's 2 pairs, two keys per lane
 #pragma unroll
     for (int rr = 0; rr < kLaPairs / kLaWarps; ++rr) {
-      const int row = warp * (kLaPairs / kLaWarps) + rr, c = ctxp[row];
+      const int row = warp * (kLaPairs / kLaWarps) + rr, c = ctxp[row], lo = lop[row];
       const int j0 = base + lane, j1 = j0 + 32;
-      const float s0 = j0 < c ? Ss[row * kSsStride + lane] * scale : -INFINITY;
-      const float s1 = j1 < c ? Ss[row * kSsStride + lane + 32] * scale : -INFINITY;
+      const bool see0 = j0 < c && j0 >= lo, see1 = j1 < c && j1 >= lo;
+      const float s0 = see0 ? Ss[row * kSsStride + lane] * scale : -INFINITY;
+      const float s1 = see1 ? Ss[row * kSsStride + lane + 32] * scale : -INFINITY;
       const float m_old = mrow[row];
       const float m_new = fmaxf(m_old, warp_max(fmaxf(s0, s1)));
       float p0 = 0.f, p1 = 0.f, cr = 1.f;
       if (m_new != -INFINITY) {
-        p0 = j0 < c ? expf(s0 - m_new) : 0.f;
-        p1 = j1 < c ? expf(s1 - m_new) : 0.f;
+        p0 = see0 ? expf(s0 - m_new) : 0.f;
+        p1 = see1 ? expf(s1 - m_new) : 0.f;
         cr = expf(m_old - m_new);
       }
       const float sum = warp_sum(p0 + p1);
@@ -295,27 +301,27 @@ int latent_attn_splits(int T, int heads, int rank, int max_ctx, int64_t ws_bytes
 
 bool latent_attn_mma_supported(int heads, int krow, int rank) {
   static const int env = getenv("B200_LATENT_MMA") ? atoi(getenv("B200_LATENT_MMA")) : 1;
-  const size_t smem = (size_t)(kLaKeys + kLaPairs) * (krow + 8) * 2 + kLaPairs * (kSsStride * 4 + kPsStride * 2 + 16);
+  const size_t smem = (size_t)(kLaKeys + kLaPairs) * (krow + 8) * 2 + kLaPairs * (kSsStride * 4 + kPsStride * 2 + 20);
   return env && heads > 0 && krow % 16 == 0 && rank % 16 == 0 && rank > 0 && rank <= 512 && rank <= krow && smem <= 200 * 1024;
 }
 
 // runs / n_runs: the run list of the step (attn_anydim.cu builds it: runs of at most 16 consecutive rows of one sequence)
 int latent_attn_mma(const float* q, const __nv_bfloat16* kc, const int32_t* block_table, int bt_stride, const int32_t* row_to_seq,
                     const int32_t* ctx_lens, __nv_bfloat16* out, const int32_t* runs, const int32_t* n_runs, int T, int heads, int krow,
-                    int rank, int block_size, float scale, const float* sink, cudaStream_t s, int n_splits, float* part) {
+                    int rank, int block_size, float scale, const float* sink, cudaStream_t s, int n_splits, float* part, int window) {
   if (T == 0) return B200_OK;
   if (n_splits < 1 || part == nullptr) n_splits = 1;
   B200_REQUIRE(n_splits <= kLaMaxSplits, B200_ERR_INVALID, "latent_attn_mma: %d splits (at most %d)", n_splits, kLaMaxSplits);
   B200_REQUIRE(latent_attn_mma_supported(heads, krow, rank), B200_ERR_UNSUPPORTED, "latent_attn_mma: shape %d / %d / %d", heads, krow, rank);
   B200_REQUIRE(reinterpret_cast<uintptr_t>(kc) % 16 == 0, B200_ERR_INVALID, "latent_attn_mma: cache not 16-byte aligned");
-  const size_t smem = (size_t)(kLaKeys + kLaPairs) * (krow + 8) * 2 + kLaPairs * (kSsStride * 4 + kPsStride * 2 + 16);
+  const size_t smem = (size_t)(kLaKeys + kLaPairs) * (krow + 8) * 2 + kLaPairs * (kSsStride * 4 + kPsStride * 2 + 20);
   const dim3 grid(T, (16 * heads + kLaPairs - 1) / kLaPairs, n_splits), block(kLaThreads);
 #define LA(NGV)                                                                                                                     \
   do {                                                                                                                              \
     static bool done[64] = {};                                                                                                      \
     if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(latent_attn_mma_kernel<NGV>, 200 * 1024, done));                            \
     B200_CUDA(launch(latent_attn_mma_kernel<NGV>, grid, block, smem, s, q, kc, block_table, bt_stride, row_to_seq, ctx_lens, out, runs, \
-                     n_runs, heads, krow, rank, block_size, scale, sink, n_splits, part));                                          \
+                     n_runs, heads, krow, rank, block_size, scale, sink, n_splits, part, window));                                          \
   } while (0)
   if (rank <= 128) LA(1);
   else if (rank <= 256) LA(2);

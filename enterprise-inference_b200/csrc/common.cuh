@@ -82,6 +82,7 @@ __device__ __forceinline__ float warp_max(float v) {
 // activations of the feed-forwards (b200_act_kind), fp32
 __device__ __forceinline__ float act_apply(float z, int kind) {
   if (kind == B200_ACT_GELU_TANH) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  if (kind == B200_ACT_RELU) return fmaxf(z, 0.f);
   if (kind == B200_ACT_RELU2) {
     const float r = fmaxf(z, 0.f);
     return r * r;
@@ -296,7 +297,7 @@ int64_t paged_attn_anydim_workspace_bytes(int T);
 int paged_attn_anydim(bool f32, const float* q, const void* kc, const void* vc, const int32_t* block_table, int bt_stride,
                       const int32_t* row_to_seq, const int32_t* ctx_lens, const int32_t* positions, const float* vrot,
                       int64_t max_pos, void* out, int T, int heads, int kv_heads, int dim, int vdim, int block_size, float scale,
-                      int plan, void* ws, cudaStream_t s, int kstride = 0, int vstride = 0, const float* sink = nullptr);
+                      int plan, void* ws, cudaStream_t s, int kstride = 0, int vstride = 0, const float* sink = nullptr, int window = 0);
 // kstride / vstride: elements per cache row when they exceed dim / vdim (0: dim / vdim; the value cache may then be the key
 // cache itself, a value being the leading vdim entries of the row); sink [heads]: exp(sink[h]) joins the softmax denominator
 int paged_attn_runs_plan(const int32_t* row_to_seq, const int32_t* ctx_lens, int T, void* ws, cudaStream_t s);
@@ -304,7 +305,8 @@ int paged_attn_runs_plan(const int32_t* row_to_seq, const int32_t* ctx_lens, int
 bool latent_attn_mma_supported(int heads, int krow, int rank);
 int latent_attn_mma(const float* q, const __nv_bfloat16* kc, const int32_t* block_table, int bt_stride, const int32_t* row_to_seq,
                     const int32_t* ctx_lens, __nv_bfloat16* out, const int32_t* runs, const int32_t* n_runs, int T, int heads, int krow,
-                    int rank, int block_size, float scale, const float* sink, cudaStream_t s, int n_splits = 1, float* part = nullptr);
+                    int rank, int block_size, float scale, const float* sink, cudaStream_t s, int n_splits = 1, float* part = nullptr,
+                    int window = 0);
 // context splits for a step (1: none); part holds T * heads * n_splits * (rank + 2) floats
 int latent_attn_splits(int T, int heads, int rank, int max_ctx, int64_t ws_bytes);
 // mixture of experts (moe.cu)
@@ -346,7 +348,7 @@ int latent_prep(bool f32, const void* qkv, int64_t ld, const float* norm_w, cons
                 const float* rot, int rot_dims, int64_t max_pos, float* qfull, void* cache, int T, int heads, int dim, int rot_dim,
                 int kv_rank, float eps, cudaStream_t s);
 int head_linear(bool f32, bool y_f32, const void* x, int64_t ldx, int x_hs, const __nv_bfloat16* w, void* y, int64_t ldy, int y_hs,
-                const void* gate, int64_t ldg, int g_hs, int T, int heads, int n_out, int k, cudaStream_t s);
+                const void* gate, int64_t ldg, int g_hs, int T, int heads, int n_out, int k, cudaStream_t s, int g_es = 1);
 int mlstm_gates(bool f32, const void* x, const __nv_bfloat16* w, const float* bias, float* out, int T, int width, int heads, float cap,
                 cudaStream_t s);
 int mlstm_col_blocks(int vd);
@@ -356,6 +358,28 @@ int mlstm_scan(bool f32, const void* qkv, int64_t ld, int q_off, int k_off, int 
                int dim, int vd, cudaStream_t s, bool single_rows = false);   // single_rows: every sequence of the step has one row
 int head_norm_gate(bool f32, const float* o, const float* w, const void* gate, int64_t ldg, void* out, int T, int heads, int vd, float eps,
                    cudaStream_t s);
+// post-norm layer form (postnorm.cu): layer norm with bias after the sum; attention whose values are its raw keys with per-head
+// q/k norms; the two norms of a latent mixer with a query latent
+int postnorm_stream(bool f32, const float* x_in, const void* y, float alpha, const float* w, const float* b, float* x_out, void* out_act,
+                    const int32_t* rows, int R, int width, float eps, cudaStream_t s);
+int qk_headnorm_rotate_cache(bool f32, const void* qk, int64_t ld, const float* qw, const float* kw, const int32_t* positions,
+                             const int32_t* slots, const float* rot, int rot_dims, int64_t max_pos, float* qout, void* kc, void* vc, int T,
+                             int heads, int kv_heads, int dim, int vdim, int block_size, float eps, cudaStream_t s);
+int latent_norms(bool f32, const void* fused, int64_t ld, int q_rank, int kv_rank, const float* qw, const float* kw, const int32_t* slots,
+                 void* cq, void* cache, int T, float eps, cudaStream_t s);
+// delta-rule recurrence with per-channel decays (delta.cu)
+int delta_fused_rows(int heads, int kv_heads, int dim, int vdim, int decay_rank, int gate_rank, int* offsets);
+int64_t delta_state_floats(int heads, int dim, int vd);
+int64_t delta_tail_floats(int heads, int kv_heads, int dim, int vd, int taps);
+int delta_prep(bool f32, const void* fused, int64_t ld, const void* a2, const float* conv_w, const float* dt_bias, const float* a_log,
+               const int32_t* positions, const int32_t* row_to_seq, const int32_t* seq_start, const int32_t* seq_slots, const float* tails,
+               int64_t slot_stride, float* qn, float* kn, float* vn, float* beta, float* decay, int T, int heads, int kv_heads, int dim,
+               int vdim, int taps, int decay_rank, int gate_rank, cudaStream_t s);
+int delta_tails(bool f32, const void* fused, int64_t ld, const int32_t* positions, const int32_t* seq_start, const int32_t* seq_slots,
+                float* tails, int64_t slot_stride, int S, int channels, int taps, cudaStream_t s);
+int delta_scan(const float* qn, const float* kn, const float* vn, const float* beta, const float* decay, const int32_t* positions,
+               const int32_t* seq_start, const int32_t* seq_slots, float* state, int64_t slot_stride, float* out, int S, int heads,
+               int kv_heads, int dim, int vd, cudaStream_t s);
 // true-fp32 CUDA-core linear (linear_simt.cu)
 int linear_simt(bool x_f32, bool y_f32, const void* x, int64_t ldx, const __nv_bfloat16* w, void* y, int64_t ldy, int T, int n_out,
                 int k, cudaStream_t s);

@@ -72,7 +72,7 @@ constexpr int kHlRows = 16;
 template <typename AT, typename YT>
 __global__ void __launch_bounds__(256)
 head_linear_kernel(const AT* __restrict__ x, int64_t ldx_, int x_hs, const __nv_bfloat16* __restrict__ w, YT* __restrict__ y, int64_t ldy,
-                   int y_hs, const AT* __restrict__ gate, int64_t ldg, int g_hs, int T, int n_out, int k) {
+                   int y_hs, const AT* __restrict__ gate, int64_t ldg, int g_hs, int g_es, int T, int n_out, int k) {
   extern __shared__ float xs[];   // [kHlRows][k]
   pdl_wait();
   pdl_launch_dependents();
@@ -98,7 +98,7 @@ head_linear_kernel(const AT* __restrict__ x, int64_t ldx_, int x_hs, const __nv_
     for (int r = 0; r < kHlRows; ++r) {
       float v = warp_sum(acc[r]);
       if (lane == 0 && r < nr) {
-        if (gate) v *= 1.0f / (1.0f + expf(-ldx<AT>(gate, (int64_t)(t0 + r) * ldg + (int64_t)h * g_hs + o)));
+        if (gate) v *= 1.0f / (1.0f + expf(-ldx<AT>(gate, (int64_t)(t0 + r) * ldg + (int64_t)h * g_hs + (int64_t)o * g_es)));
         stx<YT>(y, (int64_t)(t0 + r) * ldy + (int64_t)h * y_hs + o, v);
       }
     }
@@ -124,7 +124,7 @@ __device__ __forceinline__ void mma_bf16(float& c0, float& c1, float& c2, float&
 template <typename YT, bool VEC>
 __global__ void __launch_bounds__(128)
 head_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx_, int x_hs, const __nv_bfloat16* __restrict__ w, YT* __restrict__ y,
-                       int64_t ldy, int y_hs, const __nv_bfloat16* __restrict__ gate, int64_t ldg, int g_hs, int T, int n_out, int k) {
+                       int64_t ldy, int y_hs, const __nv_bfloat16* __restrict__ gate, int64_t ldg, int g_hs, int g_es, int T, int n_out, int k) {
   __shared__ __align__(16) __nv_bfloat16 Xs[kHmRows * kHmStride];
   __shared__ __align__(16) __nv_bfloat16 Ws[kHmOuts * kHmStride];
   pdl_wait();
@@ -193,7 +193,7 @@ head_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx_, int x_
         const int o = o0 + nt * 8 + (lane & 3) * 2 + e;
         if (o >= n_out) continue;
         float v = acc[nt][half * 2 + e];
-        if (gate) v *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(int64_t)t * ldg + (int64_t)h * g_hs + o])));
+        if (gate) v *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(int64_t)t * ldg + (int64_t)h * g_hs + (int64_t)o * g_es])));
         stx<YT>(y, (int64_t)t * ldy + (int64_t)h * y_hs + o, v);
       }
     }
@@ -219,19 +219,20 @@ int latent_prep(bool f32, const void* qkv, int64_t ld, const float* norm_w, cons
 
 template <typename AT, typename YT>
 static int head_linear_t(const void* x, int64_t ldx_, int x_hs, const __nv_bfloat16* w, void* y, int64_t ldy, int y_hs, const void* gate,
-                         int64_t ldg, int g_hs, int T, int heads, int n_out, int k, cudaStream_t s) {
+                         int64_t ldg, int g_hs, int g_es, int T, int heads, int n_out, int k, cudaStream_t s) {
   const size_t smem = (size_t)kHlRows * k * 4;
   B200_REQUIRE(smem <= 200 * 1024, B200_ERR_UNSUPPORTED, "head_linear: inner size %d does not fit shared memory", k);
   static bool done[64] = {};
   if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(head_linear_kernel<AT, YT>, 200 * 1024, done));
   B200_CUDA(launch(head_linear_kernel<AT, YT>, dim3((T + kHlRows - 1) / kHlRows, heads), dim3(256), smem, s, (const AT*)x, ldx_, x_hs, w,
-                   (YT*)y, ldy, y_hs, (const AT*)gate, ldg, g_hs, T, n_out, k));
+                   (YT*)y, ldy, y_hs, (const AT*)gate, ldg, g_hs, g_es, T, n_out, k));
   return B200_OK;
 }
 
-// x, gate: activation type (fp32 when f32, else bf16); y: fp32 when y_f32, else the activation type
+// x, gate: activation type (fp32 when f32, else bf16); y: fp32 when y_f32, else the activation type.  g_es: stride of the gate
+// inside a head (1: one gate per output, 0: one gate per head)
 int head_linear(bool f32, bool y_f32, const void* x, int64_t ldx_, int x_hs, const __nv_bfloat16* w, void* y, int64_t ldy, int y_hs,
-                const void* gate, int64_t ldg, int g_hs, int T, int heads, int n_out, int k, cudaStream_t s) {
+                const void* gate, int64_t ldg, int g_hs, int T, int heads, int n_out, int k, cudaStream_t s, int g_es) {
   if (T == 0) return B200_OK;
   static const int mma_env = getenv("B200_HEAD_LINEAR_MMA") ? atoi(getenv("B200_HEAD_LINEAR_MMA")) : 1;
   if (!f32 && mma_env && k % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0) {
@@ -239,7 +240,7 @@ int head_linear(bool f32, bool y_f32, const void* x, int64_t ldx_, int x_hs, con
     const dim3 grid((T + kHmRows - 1) / kHmRows, heads, (n_out + kHmOuts - 1) / kHmOuts), block(128);
 #define HM(YT, VEC)                                                                                                               \
   B200_CUDA(launch(head_linear_mma_kernel<YT, VEC>, grid, block, (size_t)0, s, (const __nv_bfloat16*)x, ldx_, x_hs, w, (YT*)y, ldy, y_hs, \
-                   (const __nv_bfloat16*)gate, ldg, g_hs, T, n_out, k))
+                   (const __nv_bfloat16*)gate, ldg, g_hs, g_es, T, n_out, k))
     if (y_f32) {
       if (vec) HM(float, true); else HM(float, false);
     } else {
@@ -248,9 +249,9 @@ int head_linear(bool f32, bool y_f32, const void* x, int64_t ldx_, int x_hs, con
 #undef HM
     return B200_OK;
   }
-  if (f32) return head_linear_t<float, float>(x, ldx_, x_hs, w, y, ldy, y_hs, gate, ldg, g_hs, T, heads, n_out, k, s);
-  if (y_f32) return head_linear_t<__nv_bfloat16, float>(x, ldx_, x_hs, w, y, ldy, y_hs, gate, ldg, g_hs, T, heads, n_out, k, s);
-  return head_linear_t<__nv_bfloat16, __nv_bfloat16>(x, ldx_, x_hs, w, y, ldy, y_hs, gate, ldg, g_hs, T, heads, n_out, k, s);
+  if (f32) return head_linear_t<float, float>(x, ldx_, x_hs, w, y, ldy, y_hs, gate, ldg, g_hs, g_es, T, heads, n_out, k, s);
+  if (y_f32) return head_linear_t<__nv_bfloat16, float>(x, ldx_, x_hs, w, y, ldy, y_hs, gate, ldg, g_hs, g_es, T, heads, n_out, k, s);
+  return head_linear_t<__nv_bfloat16, __nv_bfloat16>(x, ldx_, x_hs, w, y, ldy, y_hs, gate, ldg, g_hs, g_es, T, heads, n_out, k, s);
 }
 
 }  // namespace b200

@@ -18,6 +18,17 @@
 //               recurrence over the state slot;  ff(h2): dense gated, or routed experts + shared expert
 //               X_{i+1} = u + (mixer + ff);  u = sum_j dwa[j] X_j;  norms of the next layer      one kernel
 //   logit rows: u[rows] / rms * g -> W_head -> fp32 logits -> soft cap -> fp32 and bf16 copies -> argmax
+//
+// Post-norm form (b200_stack_cfg.form = B200_FORM_POSTNORM), same step entry, cache, state slots and graph replay:
+//   x = table[id]                                                         fp32 residual stream (bf16 copy for the linears)
+//   per layer:  y = mixer(x);  x = LN(alpha x + y) * w + b;   then, with a feed-forward,  x = LN'(alpha x + ff(x)) * w' + b'
+//     attention: fused q | k -> per-head RMS norm, rotation, values = raw keys into the paged cache -> windowed attention with
+//                one more unit in the denominator -> W_o
+//     latent:    fused dq | dkv | g -> two RMS norms (dkv into the cache, unless the layer reads another layer's rows) -> W_uq ->
+//                q' = W_uk^T q -> windowed attention over the latent rows -> W_uv with one sigmoid gate per head -> W_o
+//     delta:     fused q | k | v | a1 | g1 | b -> W_a2, W_g2 -> convolution, unit vectors, beta, decays -> recurrence over the
+//                state slot -> unit RMS per head, weight, gate -> W_o
+//   logit rows: LN(x[rows]) * w + b -> W_head -> fp32 logits and their bf16 copy -> argmax
 #include <math.h>
 #include <stdlib.h>
 
@@ -39,6 +50,10 @@ struct StackLayerW {
   const __nv_bfloat16 *uk_t = nullptr, *uv = nullptr, *gates = nullptr, *mlp_gate_up = nullptr, *mlp_down = nullptr,
                       *shared_up = nullptr, *shared_down = nullptr;
   int64_t tail_off = 0, rec_off = 0;   // floats from the start of a state slot: convolution tail, recurrent state
+  // post-norm form
+  const float *n_mix_post_b = nullptr, *n_mlp_post_b = nullptr, *q_lat_norm = nullptr, *conv = nullptr, *decay_bias = nullptr,
+              *decay_log = nullptr;
+  const __nv_bfloat16 *uq = nullptr, *decay_up = nullptr, *gate_up = nullptr;
 };
 
 struct StackModel {
@@ -74,12 +89,18 @@ struct StackModel {
   int32_t* seq_start = nullptr;
   float* lat_ws = nullptr;             // partial sums of the latent attention when a step's context is split over CTAs
   int64_t lat_ws_bytes = 0;
+  // post-norm form
+  const float* final_norm_b = nullptr;
+  void *cq = nullptr, *qh = nullptr, *a2 = nullptr, *g2 = nullptr;   // query latent, queries, decay and gate projections
+  float *dq = nullptr, *dk = nullptr, *dv = nullptr, *dbeta = nullptr, *ddecay = nullptr;   // what the recurrence reads
+  float* zero_sink = nullptr;          // [heads] zeros: a sink of score 0 is one more unit in the denominator
 };
 
 bool paged_attn_tc_supported(int hq, int hkv, int block_size);   // attn_tc.cu
 
 static bool is_latent(const b200_stack_layer& L) { return L.mixer == B200_MIXER_LATENT; }
 static bool is_mlstm(const b200_stack_layer& L) { return L.mixer == B200_MIXER_MLSTM; }
+static bool is_delta(const b200_stack_layer& L) { return L.mixer == B200_MIXER_DELTA; }
 
 // bf16 mode, keys and values of 64 to 128 dimensions in blocks of 128 tokens: the tcgen05 attention kernels of the fixed
 // decoder stack serve the layer.  They are built for 128-wide heads, so the layer's cache rows and its bf16 queries are
@@ -87,17 +108,17 @@ static bool is_mlstm(const b200_stack_layer& L) { return L.mixer == B200_MIXER_M
 // packing of narrower value heads are a step of their own.  Every other shape takes attn_anydim.cu.
 static bool layer_attn_tc(const b200_stack_cfg& m, const b200_stack_layer& L) {
   static const int env = getenv("B200_STACK_ATTN_TC") ? atoi(getenv("B200_STACK_ATTN_TC")) : 1;
-  return env && L.mixer == B200_MIXER_ATTENTION && !m.f32 && L.dim >= kHeadDim / 2 && L.dim <= kHeadDim && L.vdim >= kHeadDim / 2 && L.vdim <= kHeadDim &&
+  return env && L.mixer == B200_MIXER_ATTENTION && m.form == B200_FORM_SANDWICH && !m.f32 && L.dim >= kHeadDim / 2 && L.dim <= kHeadDim && L.vdim >= kHeadDim / 2 && L.vdim <= kHeadDim &&
          L.scale > 0.f && paged_attn_tc_supported(L.heads, L.kv_heads, m.block_size);
 }
 // latent mixers cache one row [latent | rotated key part] per token (no value cache); mLSTM layers cache nothing
 static int cache_kdim(const b200_stack_cfg& m, const b200_stack_layer& L) {
-  if (is_latent(L)) return L.kv_rank + L.rot_dim;
-  if (is_mlstm(L)) return 0;
+  if (is_latent(L)) return L.kv_share > 0 ? 0 : L.kv_rank + L.rot_dim;
+  if (is_mlstm(L) || is_delta(L)) return 0;
   return layer_attn_tc(m, L) ? kHeadDim : L.dim;
 }
 static int cache_vdim(const b200_stack_cfg& m, const b200_stack_layer& L) {
-  if (is_latent(L) || is_mlstm(L)) return 0;
+  if (is_latent(L) || is_mlstm(L) || is_delta(L)) return 0;
   return layer_attn_tc(m, L) ? kHeadDim : L.vdim;
 }
 
@@ -105,6 +126,10 @@ static int64_t up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
 
 // rows of the fused projection of the mixer's input
 static int qkv_rows(const b200_stack_layer& L) {
+  if (is_delta(L)) return delta_fused_rows(L.heads, L.kv_heads, L.dim, L.vdim, L.decay_rank, L.gate_rank, nullptr);
+  if (is_latent(L) && L.q_rank > 0)   // query latent | key/value latent (unless another layer's is read) | one gate row per head
+    return L.q_rank + (L.kv_share > 0 ? 0 : L.kv_rank) + ((L.mixer_flags & B200_MIXF_HEAD_GATE) ? L.heads : 0);
+  if (L.mixer == B200_MIXER_ATTENTION && (L.mixer_flags & B200_MIXF_VALUE_IS_KEY)) return (L.heads + L.kv_heads) * L.dim;
   if (is_latent(L))
     return L.heads * (L.dim + L.rot_dim) + L.kv_rank + L.rot_dim + ((L.mixer_flags & B200_MIXF_GATE) ? L.heads * L.vdim : 0);
   if (is_mlstm(L)) return 2 * L.heads * L.dim + 2 * L.heads * L.vdim;
@@ -118,7 +143,8 @@ static int stack_linear(b200_ctx* c, const void* x, int64_t ldx, const __nv_bflo
   const StackModel* M = c->stack;
   if (M->cfg.f32) return linear_simt(true, true, x, ldx, w, y, ldy, T, n_out, k, s);
   static const int tc_env = getenv("B200_STACK_TC") ? atoi(getenv("B200_STACK_TC")) : 1;
-  if (tc_env && k % 8 == 0 && ldx % 8 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0 && linear_tc_supported(T, n_out, k) &&
+  if (tc_env && k % 8 == 0 && ldx % 8 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 &&
+      linear_tc_supported(T, n_out, k) &&
       linear_tc_workspace_bytes(T, n_out, k) <= c->lin_ws_bytes)
     return linear_tc((const __nv_bfloat16*)x, ldx, w, nullptr, (__nv_bfloat16*)y, ldy, T, n_out, k, c->lin_ws, c->lin_ws_bytes,
                      nullptr, s);
@@ -155,10 +181,39 @@ static int stack_ready_parallel(const b200_ctx* c) {
   return B200_OK;
 }
 
+static int stack_ready_postnorm(const b200_ctx* c) {
+  const StackModel* M = c->stack;
+  const b200_stack_cfg& m = M->cfg;
+  B200_REQUIRE(M->final_norm_b, B200_ERR_STATE, "step: the output norm's bias is not set");
+  B200_REQUIRE(m.n_state_slots <= 0 || M->state, B200_ERR_STATE, "step: state slots not set");
+  for (size_t l = 0; l < M->layers.size(); ++l) {
+    const b200_stack_layer& L = M->layers[l];
+    const StackLayerW& W = M->w[l];
+    const int li = (int)l;
+    B200_REQUIRE(W.n_mix_post && W.n_mix_post_b && W.qkv && W.o, B200_ERR_STATE, "step: layer %d mixer weights incomplete", li);
+    if (L.mixer == B200_MIXER_ATTENTION) {
+      B200_REQUIRE(W.q_norm && W.k_norm && W.kc && W.vc, B200_ERR_STATE, "step: layer %d attention weights / cache incomplete", li);
+      B200_REQUIRE(L.rot_dims == 0 || (L.rot_table >= 0 && M->rot[L.rot_table] && M->rot_half[L.rot_table] * 2 == L.rot_dims),
+                   B200_ERR_STATE, "step: layer %d rotation table missing or of another size", li);
+    } else if (is_latent(L)) {
+      B200_REQUIRE(W.q_lat_norm && W.uq && W.uk_t && W.uv, B200_ERR_STATE, "step: layer %d latent weights incomplete", li);
+      if (L.kv_share > 0) B200_REQUIRE(M->w[L.kv_share - 1].kc, B200_ERR_STATE, "step: layer %d reads the cache of layer %d, which has none", li, L.kv_share - 1);
+      else B200_REQUIRE(W.k_norm && W.kc, B200_ERR_STATE, "step: layer %d latent norm / cache missing", li);
+    } else {
+      B200_REQUIRE(W.conv && W.decay_up && W.decay_bias && W.decay_log && W.gate_up && W.head_norm, B200_ERR_STATE,
+                   "step: layer %d recurrent weights incomplete", li);
+    }
+    if (L.mlp == B200_MLP_DENSE)
+      B200_REQUIRE(W.n_mlp_post && W.n_mlp_post_b && W.mlp_gate_up && W.mlp_down, B200_ERR_STATE, "step: layer %d feed-forward weights incomplete", li);
+  }
+  return B200_OK;
+}
+
 int stack_ready(const b200_ctx* c) {
   const StackModel* M = c->stack;
   B200_REQUIRE(M->embed && M->head && M->final_norm, B200_ERR_STATE, "step: embedding / output weights not set");
   if (M->cfg.form == B200_FORM_PARALLEL) return stack_ready_parallel(c);
+  if (M->cfg.form == B200_FORM_POSTNORM) return stack_ready_postnorm(c);
   for (size_t l = 0; l < M->layers.size(); ++l) {
     const b200_stack_layer& L = M->layers[l];
     const StackLayerW& W = M->w[l];
@@ -185,6 +240,140 @@ void stack_step_slots(const b200_ctx* c, const int32_t** seq_slots, int* n_seqs)
 void stack_destroy(b200_ctx* c) {
   delete c->stack;
   c->stack = nullptr;
+}
+
+// Logit rows of the forms that keep unrounded fp32 logits: lm_in [R][width] -> head_f32 [R][vocab] -> (cap) -> fp32 and bf16 rows
+// with the ctx's leading dimension -> argmax.
+static int stack_logits_f32(b200_ctx* c, const StepArgs& a, float cap, cudaStream_t s) {
+  StackModel* M = c->stack;
+  const b200_stack_cfg& m = M->cfg;
+  const int Wd = m.width;
+  int rc;
+  if (m.f32) {
+    rc = linear_simt(true, true, M->lm_in, Wd, M->head, M->head_f32, m.vocab, a.R, m.vocab, Wd, s);
+  } else {
+    // unrounded fp32 rows from the tcgen05 linear where it can address the operands, else the CUDA-core linear
+    static const int tc_env = getenv("B200_STACK_TC") ? atoi(getenv("B200_STACK_TC")) : 1;
+    if (tc_env && Wd % 8 == 0 && reinterpret_cast<uintptr_t>(M->head) % 16 == 0 && linear_tc_supported(a.R, m.vocab, Wd) &&
+        linear_tc_workspace_bytes(a.R, m.vocab, Wd) <= c->lin_ws_bytes) {
+      LinearExtra ex;
+      ex.mode = 4;
+      ex.out_f32 = M->head_f32;
+      rc = linear_tc((const __nv_bfloat16*)M->lm_in, Wd, M->head, nullptr, nullptr, m.vocab, a.R, m.vocab, Wd, c->lin_ws, c->lin_ws_bytes, &ex, s);
+    } else {
+      rc = linear_simt(false, true, M->lm_in, Wd, M->head, M->head_f32, m.vocab, a.R, m.vocab, Wd, s);
+    }
+  }
+  if (rc) return rc;
+  rc = logit_cap(M->head_f32, c->logits_f32, c->logits, a.R, m.vocab, c->logits_ld, cap, s);
+  if (rc) return rc;
+  rc = argmax_rows(c->logits, c->logits_ld, a.R, m.vocab, 0, a.out_tokens, nullptr, s);
+  if (rc) return rc;
+  if (a.out_logits)
+    B200_CUDA(cudaMemcpy2DAsync(a.out_logits, (size_t)m.vocab * 2, c->logits, (size_t)c->logits_ld * 2, (size_t)m.vocab * 2, a.R,
+                                cudaMemcpyDeviceToDevice, s));
+  return B200_OK;
+}
+
+// The step of the post-norm form.
+static int stack_enqueue_step_postnorm(b200_ctx* c, const StepArgs& a, cudaStream_t s) {
+  StackModel* M = c->stack;
+  const b200_stack_cfg& m = M->cfg;
+  const bool f32 = m.f32 != 0;
+  const int T = a.T, Wd = m.width, nL = m.n_layers;
+  const int64_t es = M->esz;
+  int rc;
+#define STEP(expr)     \
+  do {                 \
+    rc = (expr);       \
+    if (rc) return rc; \
+  } while (0)
+  const bool stateful = m.n_state_slots > 0;
+  const int S = a.n_seqs > 0 ? a.n_seqs : T;
+  const int32_t* seq_slots = a.seq_slots;
+  B200_REQUIRE(!stateful || seq_slots, B200_ERR_STATE, "step: the state slots of the step's sequences were not given");
+  B200_REQUIRE(S <= T, B200_ERR_INVALID, "step: %d sequences in %d rows", S, T);
+  int attn_plan = (a.row_to_seq && T >= 32 && T >= 2 * S) ? 1 : 0;
+  static const int plan_env = getenv("B200_STACK_ATTN_RUNS") ? atoi(getenv("B200_STACK_ATTN_RUNS")) : 1;
+  if (!plan_env) attn_plan = 0;
+  bool runs_built = false;   // the step's run list is in the attention workspace
+  float* x = M->x;
+  // what the linears read: the stream itself in 32-bit mode, its rounded copy otherwise
+  void* hin = f32 ? static_cast<void*>(x) : M->hn;
+  void* hcopy = f32 ? nullptr : M->hn;
+  if (stateful) STEP(seq_bounds(a.row_to_seq, T, S, M->seq_start, s));
+  STEP(embed_scaled(a.ids, M->embed, x, T, Wd, m.vocab, m.embed_scale, s, a.prev_tokens, a.n_prev));
+  if (!f32) STEP(convert_f32_to_bf16(x, (__nv_bfloat16*)M->hn, (int64_t)T * Wd, s));
+  for (int l = 0; l < nL; ++l) {
+    const b200_stack_layer& L = M->layers[l];
+    const StackLayerW& W = M->w[l];
+    const int qr = qkv_rows(L), av = L.heads * L.vdim;
+    STEP(stack_linear(c, hin, Wd, W.qkv, M->qkv, qr, T, qr, Wd, s));
+    if (L.mixer == B200_MIXER_ATTENTION) {
+      const float* rot = L.rot_dims > 0 ? M->rot[L.rot_table] : nullptr;
+      const int64_t max_pos = rot ? M->rot_pos[L.rot_table] : (1ll << 40);
+      STEP(qk_headnorm_rotate_cache(f32, M->qkv, qr, W.q_norm, W.k_norm, a.positions, a.slots, rot, L.rot_dims, max_pos, M->q, W.kc, W.vc, T,
+                                    L.heads, L.kv_heads, L.dim, L.vdim, m.block_size, m.norm_eps, s));
+      const float* sink = (L.mixer_flags & B200_MIXF_SINK_ONE) ? M->zero_sink : nullptr;
+      STEP(paged_attn_anydim(f32, M->q, W.kc, W.vc, a.block_table, a.bt_stride, a.row_to_seq, a.ctx_lens, a.positions, nullptr, max_pos,
+                             M->attn, T, L.heads, L.kv_heads, L.dim, L.vdim, m.block_size, L.scale, runs_built && attn_plan == 1 ? 2 : attn_plan,
+                             M->attn_ws, s, 0, 0, sink, L.window));
+      if (attn_plan == 1) attn_plan = 2, runs_built = true;
+    } else if (is_latent(L)) {
+      const int kr = L.kv_rank, hd = L.heads * L.dim;
+      void* cache = L.kv_share > 0 ? M->w[L.kv_share - 1].kc : W.kc;
+      STEP(latent_norms(f32, M->qkv, qr, L.q_rank, kr, W.q_lat_norm, W.k_norm, a.slots, M->cq, L.kv_share > 0 ? nullptr : W.kc, T, m.norm_eps, s));
+      STEP(stack_linear(c, M->cq, L.q_rank, W.uq, M->qh, hd, T, hd, L.q_rank, s));
+      // q' = W_uk^T q: the scores are taken against the cached latent rows
+      STEP(head_linear(f32, true, M->qh, hd, L.dim, W.uk_t, M->q, (int64_t)L.heads * kr, kr, nullptr, 0, 0, T, L.heads, kr, L.dim, s));
+      if (!f32 && latent_attn_mma_supported(L.heads, kr, kr)) {
+        if (attn_plan != 2 && !runs_built) STEP(paged_attn_runs_plan(a.row_to_seq, a.ctx_lens, T, M->attn_ws, s));
+        runs_built = true;
+        if (attn_plan == 1) attn_plan = 2;
+        const int seen = L.window > 0 ? std::min(a.max_ctx, L.window + 64) : a.max_ctx;
+        STEP(latent_attn_mma(M->q, (const __nv_bfloat16*)cache, a.block_table, a.bt_stride, a.row_to_seq, a.ctx_lens, (__nv_bfloat16*)M->lat,
+                             static_cast<const int32_t*>(M->attn_ws) + 8, static_cast<const int32_t*>(M->attn_ws), T, L.heads, kr, kr,
+                             m.block_size, L.scale, nullptr, s, latent_attn_splits(T, L.heads, kr, seen, M->lat_ws_bytes), M->lat_ws, L.window));
+      } else {
+        STEP(paged_attn_anydim(f32, M->q, cache, cache, a.block_table, a.bt_stride, a.row_to_seq, a.ctx_lens, a.positions, nullptr, 1ll << 40,
+                               M->lat, T, L.heads, 1, kr, kr, m.block_size, L.scale, runs_built && attn_plan == 1 ? 2 : attn_plan, M->attn_ws, s,
+                               kr, kr, nullptr, L.window));
+        if (attn_plan == 1) attn_plan = 2, runs_built = true;
+      }
+      const bool gate = (L.mixer_flags & B200_MIXF_HEAD_GATE) != 0;
+      const char* gptr = static_cast<const char*>(M->qkv) + (int64_t)(L.q_rank + (L.kv_share > 0 ? 0 : kr)) * es;
+      STEP(head_linear(f32, false, M->lat, (int64_t)L.heads * kr, kr, W.uv, M->attn, av, L.vdim, gate ? gptr : nullptr, qr, 1, T, L.heads,
+                       L.vdim, kr, s, 0));
+    } else {
+      int off[6];
+      delta_fused_rows(L.heads, L.kv_heads, L.dim, L.vdim, L.decay_rank, L.gate_rank, off);
+      const int hd = L.heads * L.dim, C = 2 * L.kv_heads * L.dim + av;
+      const char* fused = static_cast<const char*>(M->qkv);
+      STEP(stack_linear(c, fused + off[3] * es, qr, W.decay_up, M->a2, hd, T, hd, L.decay_rank, s));
+      STEP(stack_linear(c, fused + off[4] * es, qr, W.gate_up, M->g2, av, T, av, L.gate_rank, s));
+      float* tails = L.conv_taps > 1 ? M->state + W.tail_off : nullptr;
+      STEP(delta_prep(f32, M->qkv, qr, M->a2, W.conv, W.decay_bias, W.decay_log, a.positions, a.row_to_seq, M->seq_start, seq_slots, tails,
+                      M->slot_floats, M->dq, M->dk, M->dv, M->dbeta, M->ddecay, T, L.heads, L.kv_heads, L.dim, L.vdim, L.conv_taps,
+                      L.decay_rank, L.gate_rank, s));
+      STEP(delta_tails(f32, M->qkv, qr, a.positions, M->seq_start, seq_slots, tails, M->slot_floats, S, C, L.conv_taps, s));
+      STEP(delta_scan(M->dq, M->dk, M->dv, M->dbeta, M->ddecay, a.positions, M->seq_start, seq_slots, M->state + W.rec_off, M->slot_floats,
+                      M->oraw, S, L.heads, L.kv_heads, L.dim, L.vdim, s));
+      STEP(head_norm_gate(f32, M->oraw, W.head_norm, M->g2, av, M->attn, T, L.heads, L.vdim, m.norm_eps, s));
+    }
+    STEP(stack_linear(c, M->attn, av, W.o, M->y, Wd, T, Wd, av, s));
+    STEP(postnorm_stream(f32, x, M->y, m.residual_alpha, W.n_mix_post, W.n_mix_post_b, x, hcopy, nullptr, T, Wd, m.norm_eps, s));
+    if (L.mlp == B200_MLP_DENSE) {
+      STEP(stack_linear(c, hin, Wd, W.mlp_gate_up, M->gu, 2 * L.ff, T, 2 * L.ff, Wd, s));
+      STEP(ff_act(f32, M->gu, M->ffa, T, L.ff, true, L.act, s));
+      STEP(stack_linear(c, M->ffa, L.ff, W.mlp_down, M->y2, Wd, T, Wd, L.ff, s));
+      STEP(postnorm_stream(f32, x, M->y2, m.residual_alpha, W.n_mlp_post, W.n_mlp_post_b, x, hcopy, nullptr, T, Wd, m.norm_eps, s));
+    }
+    if (M->tap) B200_CUDA(cudaMemcpyAsync(M->tap + (int64_t)l * T * Wd, x, (size_t)T * Wd * 4, cudaMemcpyDeviceToDevice, s));
+  }
+  STEP(postnorm_stream(f32, x, nullptr, 1.0f, M->final_norm, M->final_norm_b, nullptr, M->lm_in, a.logit_rows, a.R, Wd, m.norm_eps, s));
+  STEP(stack_logits_f32(c, a, 0.f, s));
+#undef STEP
+  return B200_OK;
 }
 
 // The step of the parallel form.  Sequences of the step: a.n_seqs with their slots behind the block tables (host-buffer
@@ -302,27 +491,7 @@ static int stack_enqueue_step_parallel(b200_ctx* c, const StepArgs& a, cudaStrea
     if (M->tap) B200_CUDA(cudaMemcpyAsync(M->tap + (int64_t)l * T * Wd, u, (size_t)T * Wd * 4, cudaMemcpyDeviceToDevice, s));
   }
   STEP(rms_rows(f32, u, a.logit_rows, M->final_norm, M->lm_in, a.R, Wd, m.norm_eps, s));
-  if (f32) {
-    STEP(linear_simt(true, true, M->lm_in, Wd, M->head, M->head_f32, m.vocab, a.R, m.vocab, Wd, s));
-  } else {
-    // unrounded fp32 rows from the tcgen05 linear where it can address the operands, else the CUDA-core linear
-    static const int tc_env = getenv("B200_STACK_TC") ? atoi(getenv("B200_STACK_TC")) : 1;
-    if (tc_env && Wd % 8 == 0 && reinterpret_cast<uintptr_t>(M->head) % 16 == 0 && linear_tc_supported(a.R, m.vocab, Wd) &&
-        linear_tc_workspace_bytes(a.R, m.vocab, Wd) <= c->lin_ws_bytes) {
-      LinearExtra ex;
-      ex.mode = 4;
-      ex.out_f32 = M->head_f32;
-      STEP(linear_tc((const __nv_bfloat16*)M->lm_in, Wd, M->head, nullptr, nullptr, m.vocab, a.R, m.vocab, Wd, c->lin_ws, c->lin_ws_bytes,
-                     &ex, s));
-    } else {
-      STEP(linear_simt(false, true, M->lm_in, Wd, M->head, M->head_f32, m.vocab, a.R, m.vocab, Wd, s));
-    }
-  }
-  STEP(logit_cap(M->head_f32, c->logits_f32, c->logits, a.R, m.vocab, c->logits_ld, m.logit_softcap, s));
-  STEP(argmax_rows(c->logits, c->logits_ld, a.R, m.vocab, 0, a.out_tokens, nullptr, s));
-  if (a.out_logits)
-    B200_CUDA(cudaMemcpy2DAsync(a.out_logits, (size_t)m.vocab * 2, c->logits, (size_t)c->logits_ld * 2, (size_t)m.vocab * 2, a.R,
-                                cudaMemcpyDeviceToDevice, s));
+  STEP(stack_logits_f32(c, a, m.logit_softcap, s));
 #undef STEP
   return B200_OK;
 }
@@ -331,6 +500,7 @@ int stack_enqueue_step(b200_ctx* c, const StepArgs& a, cudaStream_t s) {
   StackModel* M = c->stack;
   const b200_stack_cfg& m = M->cfg;
   if (m.form == B200_FORM_PARALLEL) return stack_enqueue_step_parallel(c, a, s);
+  if (m.form == B200_FORM_POSTNORM) return stack_enqueue_step_postnorm(c, a, s);
   const bool f32 = m.f32 != 0;
   const int T = a.T, Wd = m.width, nL = m.n_layers;
   int rc;
@@ -429,6 +599,7 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
                    cfg->max_blocks_per_seq > 0 && cfg->max_logit_rows > 0,
                B200_ERR_INVALID, "stack_create: bad sizes");
   int max_qkv = 0, max_q = 0, max_a = 0, max_top = 0, max_exp = 0, max_ff = 0, max_lat = 0, max_gates = 0, max_gu = 0, max_ffa = 0;
+  int max_qrank = 0, max_qh = 0, max_dhd = 0, max_dqk = 0, max_dav = 0, max_dh = 0, max_heads = 0;
   int64_t moe_ws_bytes = 16;
   for (int l = 0; l < cfg->n_layers; ++l) {
     const b200_stack_layer& L = layers[l];
@@ -445,8 +616,33 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
                      "stack_create: layer %d: bad recurrent sizes (or no state slots)", l);
       B200_REQUIRE(L.mlp == B200_MLP_NONE || L.mlp == B200_MLP_MOE || L.mlp == B200_MLP_DENSE, B200_ERR_UNSUPPORTED,
                    "stack_create: layer %d: unknown feed-forward %d", l, L.mlp);
-      B200_REQUIRE(L.mlp == B200_MLP_NONE || (L.ff > 0 && L.act >= 0 && L.act <= B200_ACT_RELU2 && L.shared_ff >= 0), B200_ERR_INVALID,
+      B200_REQUIRE(L.mlp == B200_MLP_NONE || (L.ff > 0 && L.act >= 0 && L.act <= B200_ACT_RELU && L.shared_ff >= 0), B200_ERR_INVALID,
                    "stack_create: layer %d: bad feed-forward sizes", l);
+    } else if (cfg->form == B200_FORM_POSTNORM) {
+      B200_REQUIRE(L.heads > 0 && L.dim > 0 && L.vdim > 0 && L.window >= 0, B200_ERR_INVALID, "stack_create: layer %d: bad mixer sizes", l);
+      if (L.mixer == B200_MIXER_ATTENTION) {
+        B200_REQUIRE((L.mixer_flags & B200_MIXF_HEAD_NORM) && (L.mixer_flags & B200_MIXF_VALUE_IS_KEY), B200_ERR_UNSUPPORTED,
+                     "stack_create: layer %d: attention of the post-norm form has per-head norms and values that are its keys", l);
+        B200_REQUIRE(L.kv_heads > 0 && L.heads % L.kv_heads == 0 && L.dim % 2 == 0 && L.vdim <= L.dim && L.rot_dims >= 0 &&
+                         L.rot_dims <= L.dim && L.rot_dims % 2 == 0 && L.rot_table < 16,
+                     B200_ERR_INVALID, "stack_create: layer %d: bad attention sizes", l);
+      } else if (L.mixer == B200_MIXER_LATENT) {
+        B200_REQUIRE(L.kv_rank > 0 && L.q_rank > 0 && L.rot_dim == 0 && L.rot_dims == 0 && L.kv_share >= 0 && L.kv_share <= l,
+                     B200_ERR_INVALID, "stack_create: layer %d: bad latent sizes", l);
+        if (L.kv_share > 0) {
+          const b200_stack_layer& src = layers[L.kv_share - 1];
+          B200_REQUIRE(src.mixer == B200_MIXER_LATENT && src.kv_share == 0 && src.kv_rank == L.kv_rank, B200_ERR_INVALID,
+                       "stack_create: layer %d reads the latent rows of layer %d, which keeps none of that size", l, L.kv_share - 1);
+        }
+      } else if (L.mixer == B200_MIXER_DELTA) {
+        B200_REQUIRE(L.kv_heads > 0 && L.heads % L.kv_heads == 0 && L.dim <= 256 && L.conv_taps >= 1 && L.conv_taps <= 64 &&
+                         L.decay_rank > 0 && L.gate_rank > 0 && cfg->n_state_slots > 0,
+                     B200_ERR_INVALID, "stack_create: layer %d: bad recurrent sizes (or no state slots)", l);
+      } else {
+        B200_REQUIRE(false, B200_ERR_UNSUPPORTED, "stack_create: layer %d: mixer %d is not served in the post-norm form", l, L.mixer);
+      }
+      B200_REQUIRE(L.mlp == B200_MLP_NONE || (L.mlp == B200_MLP_DENSE && L.ff > 0 && L.act >= 0 && L.act <= B200_ACT_RELU), B200_ERR_UNSUPPORTED,
+                   "stack_create: layer %d: the post-norm form has dense feed-forwards", l);
     } else {
     B200_REQUIRE(L.mixer == B200_MIXER_ATTENTION, B200_ERR_UNSUPPORTED, "stack_create: layer %d: unknown mixer %d", l, L.mixer);
     B200_REQUIRE(L.heads > 0 && L.kv_heads > 0 && L.heads % L.kv_heads == 0 && L.dim > 0 && L.vdim > 0 && L.dim % 2 == 0 &&
@@ -472,10 +668,18 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
     max_a = std::max(max_a, L.heads * L.vdim);
     if (is_latent(L)) max_lat = std::max(max_lat, L.heads * L.kv_rank);
     if (is_mlstm(L)) max_gates = std::max(max_gates, 2 * L.heads);
+    max_heads = std::max(max_heads, L.heads);
+    if (is_latent(L) && L.q_rank > 0) max_qrank = std::max(max_qrank, L.q_rank), max_qh = std::max(max_qh, L.heads * L.dim);
+    if (is_delta(L)) {
+      max_dhd = std::max(max_dhd, L.heads * L.dim);
+      max_dqk = std::max(max_dqk, L.kv_heads * L.dim);
+      max_dav = std::max(max_dav, L.heads * L.vdim);
+      max_dh = std::max(max_dh, L.heads);
+    }
     if (L.mlp == B200_MLP_DENSE) max_gu = std::max(max_gu, 2 * L.ff), max_ffa = std::max(max_ffa, L.ff);
     if (L.shared_ff > 0) max_gu = std::max(max_gu, 2 * L.shared_ff), max_ffa = std::max(max_ffa, L.shared_ff);
   }
-  const bool par = cfg->form == B200_FORM_PARALLEL;
+  const bool par = cfg->form == B200_FORM_PARALLEL, post = cfg->form == B200_FORM_POSTNORM;
   B200_REQUIRE(par || (!cfg->canon_taps && !cfg->depth_avg && !cfg->bigram_buckets && cfg->logit_softcap == 0.f), B200_ERR_UNSUPPORTED,
                "stack_create: convolution, depth average, bigram rows and the logit cap belong to the parallel form");
   B200_REQUIRE(!par || (cfg->canon_taps >= 0 && cfg->canon_taps <= 8 && cfg->n_state_slots >= 0 &&
@@ -503,6 +707,19 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
       off = up(off, 4);
     }
     M->slot_floats = off;
+  }
+  if (post && cfg->n_state_slots > 0) {
+    // one slot: per delta layer the convolution tail [taps - 1][q | k | v channels], then the state [heads][vdim][dim]
+    int64_t off = 0;
+    for (int l = 0; l < cfg->n_layers; ++l) {
+      const b200_stack_layer& L = layers[l];
+      if (!is_delta(L)) continue;
+      M->w[l].tail_off = off;
+      off = up(off + delta_tail_floats(L.heads, L.kv_heads, L.dim, L.vdim, L.conv_taps), 4);
+      M->w[l].rec_off = off;
+      off = up(off + delta_state_floats(L.heads, L.dim, L.vdim), 4);
+    }
+    M->slot_floats = std::max<int64_t>(off, 4);
   }
   b200_model_cfg& mc = c->cfg;
   memset(&mc, 0, sizeof(mc));
@@ -545,6 +762,11 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
         shapes.push_back({(layers[l].ungated ? 1 : 2) * layers[l].shared_ff, (int)Wd});
         shapes.push_back({(int)Wd, layers[l].shared_ff});
       }
+      if (is_latent(layers[l]) && layers[l].q_rank > 0) shapes.push_back({layers[l].heads * layers[l].dim, layers[l].q_rank});
+      if (is_delta(layers[l])) {
+        shapes.push_back({layers[l].heads * layers[l].dim, layers[l].decay_rank});
+        shapes.push_back({layers[l].heads * layers[l].vdim, layers[l].gate_rank});
+      }
     }
     for (auto& sh : shapes) {
       if (sh.second % 8) continue;
@@ -577,7 +799,7 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
   }
 
   M->lat_ws_bytes = 16;
-  if (par && !cfg->f32)
+  if ((par || post) && !cfg->f32)
     for (int l = 0; l < cfg->n_layers; ++l)
       if (is_latent(layers[l]) && latent_attn_mma_supported(layers[l].heads, layers[l].kv_rank + layers[l].rot_dim, layers[l].kv_rank))
         // splitting only happens below one CTA per SM: at most 148 * 16 pairs, 16 splits
@@ -603,19 +825,29 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
       {(void**)&M->attn_tc_ws, M->attn_tc_ws_bytes},
       {(void**)&M->attn_wide, tc_heads ? T * tc_heads * kHeadDim * 2 : 16},
       {(void**)&c->logits, R * (int64_t)c->logits_ld * 2},
-      {(void**)&c->logits_f32, (cfg->f32 || par) ? R * (int64_t)c->logits_ld * 4 : 16},
+      {(void**)&c->logits_f32, (cfg->f32 || par || post) ? R * (int64_t)c->logits_ld * 4 : 16},
       {(void**)&M->results, par && cfg->depth_avg ? (int64_t)(cfg->n_layers + 1) * T * Wd * 4 : 16},
       {(void**)&M->h1f, par && cfg->canon_taps >= 1 ? T * Wd * 4 : 16},
       {(void**)&M->hc, par ? T * Wd * es : 16},
       {(void**)&M->lat, T * std::max(max_lat, 1) * es},
-      {(void**)&M->y2, par ? T * Wd * es : 16},
+      {(void**)&M->y2, (par || post) ? T * Wd * es : 16},
       {(void**)&M->y3, par ? T * Wd * es : 16},
       {(void**)&M->gu, T * std::max(max_gu, 1) * es},
       {(void**)&M->ffa, T * std::max(max_ffa, 1) * es},
       {(void**)&M->gates_buf, T * std::max(max_gates, 1) * 4},
-      {(void**)&M->oraw, max_gates ? T * max_a * 4 : 16},
-      {(void**)&M->head_f32, par ? R * (int64_t)cfg->vocab * 4 : 16},
+      {(void**)&M->oraw, (max_gates || max_dav) ? T * max_a * 4 : 16},
+      {(void**)&M->head_f32, (par || post) ? R * (int64_t)cfg->vocab * 4 : 16},
       {(void**)&M->seq_start, (T + 2) * 4},
+      {(void**)&M->cq, T * std::max(max_qrank, 1) * es},
+      {(void**)&M->qh, T * std::max(max_qh, 1) * es},
+      {(void**)&M->a2, T * std::max(max_dhd, 1) * es},
+      {(void**)&M->g2, T * std::max(max_dav, 1) * es},
+      {(void**)&M->dq, T * std::max(max_dqk, 1) * 4},
+      {(void**)&M->dk, T * std::max(max_dqk, 1) * 4},
+      {(void**)&M->dv, T * std::max(max_dav, 1) * 4},
+      {(void**)&M->dbeta, T * std::max(max_dh, 1) * 4},
+      {(void**)&M->ddecay, T * std::max(max_dhd, 1) * 4},
+      {(void**)&M->zero_sink, std::max(max_heads, 1) * 4},
       {(void**)&M->lat_ws, M->lat_ws_bytes},
       {(void**)&c->lin_ws, c->lin_ws_bytes},
       {(void**)&c->d_meta, c->meta_ints * 4},
@@ -642,7 +874,7 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
     *it.p = static_cast<char*>(c->pool) + off;
     off += up(std::max<int64_t>(it.bytes, 16), 1024);
   }
-  if (!cfg->f32 && !par) c->logits_f32 = nullptr;
+  if (!cfg->f32 && !par && !post) c->logits_f32 = nullptr;
   *out = c;
   return B200_OK;
 }
@@ -654,7 +886,9 @@ extern "C" int b200_stack_set_weight(b200_ctx* c, int32_t layer, int32_t kind, c
   const int64_t Wd = M->cfg.width, V = M->cfg.vocab;
   int64_t er = 0, ec = 1;
   const bool par = M->cfg.form == B200_FORM_PARALLEL;
-  const bool global = kind == B200_SW_EMBED || kind == B200_SW_FINAL_NORM || kind == B200_SW_HEAD || kind == B200_SW_BIGRAM;
+  const bool post = M->cfg.form == B200_FORM_POSTNORM;
+  const bool global = kind == B200_SW_EMBED || kind == B200_SW_FINAL_NORM || kind == B200_SW_HEAD || kind == B200_SW_BIGRAM ||
+                      kind == B200_SW_FINAL_NORM_BIAS;
   if (!global) B200_REQUIRE(layer >= 0 && layer < M->cfg.n_layers, B200_ERR_INVALID, "stack_set_weight: layer %d out of range", layer);
   const b200_stack_layer L = global ? b200_stack_layer{} : M->layers[layer];
   switch (kind) {
@@ -662,8 +896,16 @@ extern "C" int b200_stack_set_weight(b200_ctx* c, int32_t layer, int32_t kind, c
     case B200_SW_FINAL_NORM: case B200_SW_NORM_MIX_PRE: case B200_SW_NORM_MIX_POST: case B200_SW_NORM_MLP_PRE:
     case B200_SW_NORM_MLP_POST: er = par ? 1 : Wd; break;
     case B200_SW_QKV: er = qkv_rows(L); ec = Wd; break;
-    case B200_SW_Q_NORM: er = (int64_t)L.heads * L.dim; break;
-    case B200_SW_K_NORM: er = is_latent(L) ? L.kv_rank : (int64_t)L.kv_heads * L.dim; break;
+    case B200_SW_Q_NORM: er = (L.mixer_flags & B200_MIXF_HEAD_NORM) ? L.dim : (int64_t)L.heads * L.dim; break;
+    case B200_SW_K_NORM: er = is_latent(L) ? L.kv_rank : ((L.mixer_flags & B200_MIXF_HEAD_NORM) ? L.dim : (int64_t)L.kv_heads * L.dim); break;
+    case B200_SW_NORM_MIX_POST_BIAS: case B200_SW_NORM_MLP_POST_BIAS: case B200_SW_FINAL_NORM_BIAS: er = Wd; break;
+    case B200_SW_Q_LATENT_NORM: er = L.q_rank; break;
+    case B200_SW_UQ: er = (int64_t)L.heads * L.dim; ec = L.q_rank; break;
+    case B200_SW_CONV: er = 2 * (int64_t)L.kv_heads * L.dim + (int64_t)L.heads * L.vdim; ec = L.conv_taps; break;
+    case B200_SW_DECAY_UP: er = (int64_t)L.heads * L.dim; ec = L.decay_rank; break;
+    case B200_SW_DECAY_BIAS: er = (int64_t)L.heads * L.dim; break;
+    case B200_SW_DECAY_LOG: er = L.heads; break;
+    case B200_SW_GATE_UP: er = (int64_t)L.heads * L.vdim; ec = L.gate_rank; break;
     case B200_SW_O: er = Wd; ec = (int64_t)L.heads * L.vdim; break;
     case B200_SW_ROUTER: er = L.experts; ec = Wd; break;
     case B200_SW_ROUTER_BIAS: er = L.experts; break;
@@ -684,11 +926,16 @@ extern "C" int b200_stack_set_weight(b200_ctx* c, int32_t layer, int32_t kind, c
     case B200_SW_SHARED_DOWN: er = Wd; ec = L.shared_ff; break;
     default: B200_REQUIRE(false, B200_ERR_INVALID, "stack_set_weight: unknown kind %d", kind);
   }
-  B200_REQUIRE(kind < B200_SW_BIGRAM || par, B200_ERR_INVALID, "stack_set_weight: kind %d belongs to the parallel form", kind);
+  B200_REQUIRE(kind < B200_SW_BIGRAM || par || post, B200_ERR_INVALID, "stack_set_weight: kind %d belongs to another layer form", kind);
+  B200_REQUIRE(kind < B200_SW_NORM_MIX_POST_BIAS || post, B200_ERR_INVALID, "stack_set_weight: kind %d belongs to the post-norm form", kind);
+  if (kind == B200_SW_Q_LATENT_NORM || kind == B200_SW_UQ)
+    B200_REQUIRE(is_latent(L) && L.q_rank > 0, B200_ERR_INVALID, "stack_set_weight: layer %d has no query latent", layer);
+  if (kind >= B200_SW_CONV && kind <= B200_SW_GATE_UP)
+    B200_REQUIRE(is_delta(L), B200_ERR_INVALID, "stack_set_weight: layer %d has no delta recurrence", layer);
   if (kind == B200_SW_UK_T || kind == B200_SW_UV || kind == B200_SW_SINK)
     B200_REQUIRE(is_latent(L), B200_ERR_INVALID, "stack_set_weight: layer %d has no latent attention", layer);
   if (kind == B200_SW_GATES || kind == B200_SW_GATES_BIAS || kind == B200_SW_HEAD_NORM)
-    B200_REQUIRE(is_mlstm(L), B200_ERR_INVALID, "stack_set_weight: layer %d has no recurrence", layer);
+    B200_REQUIRE(is_mlstm(L) || (is_delta(L) && kind == B200_SW_HEAD_NORM), B200_ERR_INVALID, "stack_set_weight: layer %d has no recurrence", layer);
   if (kind == B200_SW_MLP_GATE_UP || kind == B200_SW_MLP_DOWN)
     B200_REQUIRE(L.mlp == B200_MLP_DENSE, B200_ERR_INVALID, "stack_set_weight: layer %d has no dense feed-forward", layer);
   B200_REQUIRE(rows == er && cols == ec, B200_ERR_INVALID, "stack_set_weight: kind %d of layer %d expects [%lld,%lld], got [%lld,%lld]",
@@ -727,6 +974,16 @@ extern "C" int b200_stack_set_weight(b200_ctx* c, int32_t layer, int32_t kind, c
     case B200_SW_MLP_DOWN: M->w[layer].mlp_down = b; break;
     case B200_SW_SHARED_UP: M->w[layer].shared_up = b; break;
     case B200_SW_SHARED_DOWN: M->w[layer].shared_down = b; break;
+    case B200_SW_NORM_MIX_POST_BIAS: M->w[layer].n_mix_post_b = f; break;
+    case B200_SW_NORM_MLP_POST_BIAS: M->w[layer].n_mlp_post_b = f; break;
+    case B200_SW_FINAL_NORM_BIAS: M->final_norm_b = f; break;
+    case B200_SW_Q_LATENT_NORM: M->w[layer].q_lat_norm = f; break;
+    case B200_SW_UQ: M->w[layer].uq = b; break;
+    case B200_SW_CONV: M->w[layer].conv = f; break;
+    case B200_SW_DECAY_UP: M->w[layer].decay_up = b; break;
+    case B200_SW_DECAY_BIAS: M->w[layer].decay_bias = f; break;
+    case B200_SW_DECAY_LOG: M->w[layer].decay_log = f; break;
+    case B200_SW_GATE_UP: M->w[layer].gate_up = b; break;
   }
   return B200_OK;
 }
@@ -1017,4 +1274,89 @@ extern "C" int b200_latent_attn(const float* q, const void* cache, const int32_t
   return latent_attn_mma(q, (const __nv_bfloat16*)cache, block_table, bt_stride, row_to_seq, ctx_lens, (__nv_bfloat16*)out,
                          static_cast<const int32_t*>(workspace) + 8, static_cast<const int32_t*>(workspace), T, heads, k_row, rank,
                          block_size, scale, sink, (cudaStream_t)stream, n_splits, part);
+}
+
+// ---- per-kernel entry points of the post-norm form ---------------------------------------------------------------------------
+extern "C" int32_t b200_delta_fused_rows(int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim, int32_t decay_rank, int32_t gate_rank,
+                                         int32_t* offsets) {
+  return delta_fused_rows(heads, kv_heads, dim, vdim, decay_rank, gate_rank, offsets);
+}
+
+extern "C" int b200_postnorm_stream(int32_t f32, const float* x_in, const void* y, float alpha, const float* w, const float* b, float* x_out,
+                                    void* out_act, const int32_t* rows, int32_t R, int32_t width, float eps, void* stream) {
+  B200_REQUIRE(x_in && w && width > 0 && R >= 0, B200_ERR_INVALID, "postnorm_stream: bad argument");
+  return postnorm_stream(f32 != 0, x_in, y, alpha, w, b, x_out, out_act, rows, R, width, eps, (cudaStream_t)stream);
+}
+
+extern "C" int b200_qk_headnorm_rotate_cache(int32_t f32, const void* qk, int64_t ld, const float* qw, const float* kw, const int32_t* positions,
+                                             const int32_t* slots, const float* rot, int32_t rot_dims, int64_t max_pos, float* q_out, void* kc,
+                                             void* vc, int32_t T, int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim, int32_t block_size,
+                                             float eps, void* stream) {
+  B200_REQUIRE(qk && qw && kw && positions && slots && q_out && kc && vc && heads > 0 && kv_heads > 0 && dim > 0 && block_size > 0 && max_pos > 0,
+               B200_ERR_INVALID, "qk_headnorm_rotate_cache: bad argument");
+  return qk_headnorm_rotate_cache(f32 != 0, qk, ld, qw, kw, positions, slots, rot, rot ? rot_dims : 0, max_pos, q_out, kc, vc, T, heads, kv_heads,
+                                  dim, vdim, block_size, eps, (cudaStream_t)stream);
+}
+
+extern "C" int b200_paged_attn_window(int32_t f32, const float* q, const void* kc, const void* vc, const int32_t* block_table, int32_t bt_stride,
+                                      const int32_t* row_to_seq, const int32_t* ctx_lens, const int32_t* positions, void* out, int32_t T,
+                                      int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim, int32_t block_size, float scale,
+                                      int32_t shared_tiles, void* ws, int32_t k_row, int32_t v_row, const float* sink, int32_t window,
+                                      void* stream) {
+  B200_REQUIRE(q && kc && vc && block_table && ctx_lens && positions && out && block_size > 0 && window >= 0, B200_ERR_INVALID,
+               "paged_attn_window: bad argument");
+  B200_REQUIRE(!shared_tiles || ws, B200_ERR_INVALID, "paged_attn_window: the shared-tile form needs its workspace");
+  return paged_attn_anydim(f32 != 0, q, kc, vc, block_table, bt_stride, row_to_seq, ctx_lens, positions, nullptr, 1ll << 40, out, T, heads,
+                           kv_heads, dim, vdim, block_size, scale, shared_tiles ? 1 : 0, ws, (cudaStream_t)stream, k_row, v_row, sink, window);
+}
+
+extern "C" int b200_latent_attn_window(const float* q, const void* cache, const int32_t* block_table, int32_t bt_stride,
+                                       const int32_t* row_to_seq, const int32_t* ctx_lens, void* out, int32_t T, int32_t heads, int32_t k_row,
+                                       int32_t rank, int32_t block_size, float scale, const float* sink, void* workspace, int32_t window,
+                                       void* stream) {
+  B200_REQUIRE(q && cache && block_table && ctx_lens && out && workspace && block_size > 0 && window >= 0, B200_ERR_INVALID,
+               "latent_attn_window: bad argument");
+  int rc = paged_attn_runs_plan(row_to_seq, ctx_lens, T, workspace, (cudaStream_t)stream);
+  if (rc) return rc;
+  return latent_attn_mma(q, (const __nv_bfloat16*)cache, block_table, bt_stride, row_to_seq, ctx_lens, (__nv_bfloat16*)out,
+                         static_cast<const int32_t*>(workspace) + 8, static_cast<const int32_t*>(workspace), T, heads, k_row, rank,
+                         block_size, scale, sink, (cudaStream_t)stream, 1, nullptr, window);
+}
+
+extern "C" int b200_latent_norms(int32_t f32, const void* fused, int64_t ld, int32_t q_rank, int32_t kv_rank, const float* qw, const float* kw,
+                                 const int32_t* slots, void* cq, void* cache, int32_t T, float eps, void* stream) {
+  B200_REQUIRE(fused && q_rank >= 0 && kv_rank >= 0, B200_ERR_INVALID, "latent_norms: bad argument");
+  return latent_norms(f32 != 0, fused, ld, q_rank, kv_rank, qw, kw, slots, cq, cache, T, eps, (cudaStream_t)stream);
+}
+
+extern "C" int b200_head_linear_head_gate(int32_t f32, const void* x, int64_t ldx, int32_t x_hs, const void* w, void* y, int64_t ldy, int32_t y_hs,
+                                          const void* gate, int64_t ldg, int32_t T, int32_t heads, int32_t n_out, int32_t k, void* stream) {
+  B200_REQUIRE(x && w && y && gate && heads > 0 && n_out > 0 && k > 0, B200_ERR_INVALID, "head_linear_head_gate: bad argument");
+  return head_linear(f32 != 0, false, x, ldx, x_hs, (const __nv_bfloat16*)w, y, ldy, y_hs, gate, ldg, 1, T, heads, n_out, k, (cudaStream_t)stream, 0);
+}
+
+extern "C" int b200_delta_prep(int32_t f32, const void* fused, int64_t ld, const void* a2, const float* conv_w, const float* dt_bias,
+                               const float* a_log, const int32_t* positions, const int32_t* row_to_seq, const int32_t* seq_start,
+                               const int32_t* seq_slots, const float* tails, int64_t slot_stride, float* qn, float* kn, float* vn, float* beta,
+                               float* decay, int32_t T, int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim, int32_t taps,
+                               int32_t decay_rank, int32_t gate_rank, void* stream) {
+  B200_REQUIRE(fused && a2 && conv_w && dt_bias && a_log && positions && seq_start && qn && kn && vn && beta && decay, B200_ERR_INVALID,
+               "delta_prep: null argument");
+  return delta_prep(f32 != 0, fused, ld, a2, conv_w, dt_bias, a_log, positions, row_to_seq, seq_start, seq_slots, tails, slot_stride, qn, kn, vn,
+                    beta, decay, T, heads, kv_heads, dim, vdim, taps, decay_rank, gate_rank, (cudaStream_t)stream);
+}
+
+extern "C" int b200_delta_tails(int32_t f32, const void* fused, int64_t ld, const int32_t* positions, const int32_t* seq_start,
+                                const int32_t* seq_slots, float* tails, int64_t slot_stride, int32_t S, int32_t channels, int32_t taps,
+                                void* stream) {
+  B200_REQUIRE(fused && channels > 0 && taps >= 1, B200_ERR_INVALID, "delta_tails: bad argument");
+  return delta_tails(f32 != 0, fused, ld, positions, seq_start, seq_slots, tails, slot_stride, S, channels, taps, (cudaStream_t)stream);
+}
+
+extern "C" int b200_delta_scan(const float* qn, const float* kn, const float* vn, const float* beta, const float* decay, const int32_t* positions,
+                               const int32_t* seq_start, const int32_t* seq_slots, float* state, int64_t slot_stride, float* out, int32_t S,
+                               int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim, void* stream) {
+  B200_REQUIRE(qn && kn && vn && beta && decay && out, B200_ERR_INVALID, "delta_scan: null argument");
+  return delta_scan(qn, kn, vn, beta, decay, positions, seq_start, seq_slots, state, slot_stride, out, S, heads, kv_heads, dim, vdim,
+                    (cudaStream_t)stream);
 }

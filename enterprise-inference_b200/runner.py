@@ -435,14 +435,34 @@ class StackRunner(ModelRunner):
                 self._tables.append(spec.table(max(max_model_len, 16)).to(self.device))
             return keys[k]
 
-        from .config import DupolornConfig, MLSTMSpec
+        from .config import AttentionSpec, ChannelDeltaSpec, DupolornConfig, FutidraConfig, MLSTMSpec
         self.parallel = isinstance(cfg, DupolornConfig)
-        self.n_state_slots = int(n_state_slots) if self.parallel and cfg.needs_state else 0
-        if self.parallel and cfg.needs_state and self.n_state_slots <= 0:
+        self.postnorm = isinstance(cfg, FutidraConfig)
+        stateful = (self.parallel or self.postnorm) and cfg.needs_state
+        self.n_state_slots = int(n_state_slots) if stateful else 0
+        if stateful and self.n_state_slots <= 0:
             raise ValueError("this model keeps per-sequence state: n_state_slots must be positive")
         layers = (_abi.StackLayer * cfg.n_layers)()
         for i, L in enumerate(cfg.layers):
             a, f = L.mixer, L.mlp
+            if self.postnorm:
+                if isinstance(a, AttentionSpec):
+                    flags = (_abi.MIXF_HEAD_NORM if a.head_norm else 0) | (_abi.MIXF_VALUE_IS_KEY if a.value_is_key else 0) | \
+                            (_abi.MIXF_SINK_ONE if a.sink_one else 0)
+                    d = dict(mixer=_abi.MIXER_ATTENTION, heads=a.heads, kv_heads=a.kv_heads, dim=a.dim, vdim=a.vdim,
+                             rot_dims=a.rot.dims if a.rot else 0, rot_table=table_of(a.rot), vrot_table=-1, scale=a.scale,
+                             mixer_flags=flags, window=a.window)
+                elif isinstance(a, ChannelDeltaSpec):
+                    d = dict(mixer=_abi.MIXER_DELTA, heads=a.heads, kv_heads=a.kv_heads, dim=a.dim, vdim=a.vdim, rot_table=-1, vrot_table=-1,
+                             conv_taps=a.conv, decay_rank=a.decay_rank, gate_rank=a.gate_rank)
+                else:
+                    d = dict(mixer=_abi.MIXER_LATENT, heads=a.heads, kv_heads=1, dim=a.dim, vdim=a.vdim, rot_table=-1, vrot_table=-1,
+                             scale=a.scale, kv_rank=a.kv_rank, q_rank=a.q_rank, window=a.window,
+                             mixer_flags=_abi.MIXF_HEAD_GATE if a.head_gate else 0, kv_share=0 if a.kv_from is None else a.kv_from + 1)
+                if f is not None:
+                    d.update(mlp=_abi.MLP_DENSE, ff=f.ff, act=_abi.ACTS[f.act])
+                layers[i] = _abi.StackLayer(**d)
+                continue
             if not self.parallel:
                 layers[i] = _abi.StackLayer(
                     mixer=_abi.MIXER_ATTENTION, heads=a.heads, kv_heads=a.kv_heads, dim=a.dim, vdim=a.vdim,
@@ -470,6 +490,8 @@ class StackRunner(ModelRunner):
             sc.form, sc.canon_taps, sc.depth_avg = _abi.FORM_PARALLEL, cfg.canon_taps, int(cfg.depth_avg)
             sc.bigram_buckets, sc.bigram_mul_prev, sc.bigram_mul_cur = cfg.bigram_buckets, cfg.bigram_mul_prev, cfg.bigram_mul_cur
             sc.logit_softcap, sc.n_state_slots = cfg.logit_softcap, self.n_state_slots
+        if self.postnorm:
+            sc.form, sc.residual_alpha, sc.n_state_slots = _abi.FORM_POSTNORM, cfg.postln_alpha, self.n_state_slots
         h = C.c_void_p()
         _abi.check(self.lib.b200_stack_create(C.byref(sc), layers, C.byref(h)))
         self.ctx = h

@@ -168,4 +168,66 @@ def dupolorn_weights(w: Dict[str, torch.Tensor], cfg) -> Iterator[Tuple[int, int
                 yield i, A.SW_SHARED_DOWN, w[p + "mlp.shared.down"]
 
 
-STACK_WEIGHT_MAPS = {"Bopilorn": bopilorn_weights, "Dupolorn": dupolorn_weights}
+def delta_fused_offsets(a) -> Tuple[int, list]:
+    """(rows, [q, k, v, a1, g1, b offsets]) of the delta mixer's fused projection: the three small groups start at multiples of 8
+    rows and the total is a multiple of 8 (the rows between are zeros), as b200_delta_fused_rows lays them out."""
+    up8 = lambda v: (v + 7) // 8 * 8
+    o = [0, a.kv_heads * a.dim, 2 * a.kv_heads * a.dim]
+    o.append(up8(o[2] + a.heads * a.vdim))
+    o.append(up8(o[3] + a.decay_rank))
+    o.append(up8(o[4] + a.gate_rank))
+    return up8(o[5] + a.heads), o
+
+
+def futidra_weights(w: Dict[str, torch.Tensor], cfg) -> Iterator[Tuple[int, int, torch.Tensor]]:
+    """(layer, b200_stack_weight kind, tensor) of a Futidra checkpoint: `embed` (also the output projection), `final.norm[.b]`, per
+    layer i `l<i>.norm1[.b]`, `l<i>.norm2[.b]`, the mixer `l<i>.mix.*` and the feed-forward `l<i>.mlp.gate|up|down`.  Projections
+    of the mixer's input are fused row-wise: attention q | k; latent dq | dkv | g (no dkv where the layer reads another layer's
+    latents); delta q | k | v | a1 | g1 | b with zero rows so that a1, g1 and b start at multiples of 8.  A latent head's key
+    expansion goes over transposed ([heads][kv_rank][dim]); the delta mixer's head norm weight is repeated for every head; the
+    three convolution kernels are stacked; vectors go over in fp32."""
+    from . import _abi as A
+    from .config import AttentionSpec, ChannelDeltaSpec
+    yield 0, A.SW_EMBED, w["embed"]
+    yield 0, A.SW_HEAD, w["embed"]
+    yield 0, A.SW_FINAL_NORM, w["final.norm"]
+    yield 0, A.SW_FINAL_NORM_BIAS, w["final.norm.b"]
+    for i, L in enumerate(cfg.layers):
+        p, a, f = f"l{i}.", L.mixer, L.mlp
+        yield i, A.SW_NORM_MIX_POST, w[p + "norm1"]
+        yield i, A.SW_NORM_MIX_POST_BIAS, w[p + "norm1.b"]
+        if isinstance(a, AttentionSpec):
+            yield i, A.SW_QKV, torch.cat([w[p + "mix.q"], w[p + "mix.k"]], 0)
+            yield i, A.SW_Q_NORM, w[p + "mix.q.norm"]
+            yield i, A.SW_K_NORM, w[p + "mix.k.norm"]
+        elif isinstance(a, ChannelDeltaSpec):
+            rows, o = delta_fused_offsets(a)
+            fused = torch.zeros((rows, cfg.width), dtype=w[p + "mix.q"].dtype)
+            for off, name in zip(o, ("q", "k", "v", "a1", "g1", "b")):
+                t = w[p + "mix." + name]
+                fused[off:off + t.shape[0]] = t
+            yield i, A.SW_QKV, fused
+            yield i, A.SW_CONV, torch.cat([w[p + "mix.q.conv"], w[p + "mix.k.conv"], w[p + "mix.v.conv"]], 0)
+            yield i, A.SW_DECAY_UP, w[p + "mix.a2"]
+            yield i, A.SW_DECAY_BIAS, w[p + "mix.dt_bias"]
+            yield i, A.SW_DECAY_LOG, w[p + "mix.A_log"]
+            yield i, A.SW_GATE_UP, w[p + "mix.g2"]
+            yield i, A.SW_HEAD_NORM, w[p + "mix.norm"].repeat(a.heads)
+        else:
+            own = a.kv_from is None
+            yield i, A.SW_QKV, torch.cat([w[p + "mix.dq"]] + ([w[p + "mix.dkv"]] if own else []) + [w[p + "mix.g"]], 0)
+            yield i, A.SW_Q_LATENT_NORM, w[p + "mix.dq.norm"]
+            yield i, A.SW_UQ, w[p + "mix.uq"]
+            if own:
+                yield i, A.SW_K_NORM, w[p + "mix.dkv.norm"]
+            yield i, A.SW_UK_T, w[p + "mix.uk"].reshape(a.heads, a.dim, a.kv_rank).transpose(1, 2).reshape(a.heads * a.kv_rank, a.dim)
+            yield i, A.SW_UV, w[p + "mix.uv"]
+        yield i, A.SW_O, w[p + "mix.o"]
+        if f is not None:
+            yield i, A.SW_NORM_MLP_POST, w[p + "norm2"]
+            yield i, A.SW_NORM_MLP_POST_BIAS, w[p + "norm2.b"]
+            yield i, A.SW_MLP_GATE_UP, torch.cat([w[p + "mlp.gate"], w[p + "mlp.up"]], 0)
+            yield i, A.SW_MLP_DOWN, w[p + "mlp.down"]
+
+
+STACK_WEIGHT_MAPS = {"Bopilorn": bopilorn_weights, "Dupolorn": dupolorn_weights, "Futidra": futidra_weights}

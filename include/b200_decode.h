@@ -390,12 +390,30 @@ B200_API int b200_tp_allreduce(b200_ctx* ctx, int32_t buf_idx, const void* parti
  * with q scaled by dim^-1/2; each head's o is brought to unit RMS, times a weight, times sigmoid(W_g h).
  *
  * B200_MLP_DENSE: down(act(gate x) * (up x)).  Routed experts of this form may score with a sigmoid, apply the mixing
- * weight to the expert's INPUT, be ungated (down(act(up x))), and come with one shared expert of the same shape. */
-typedef enum b200_mixer_kind { B200_MIXER_ATTENTION = 1, B200_MIXER_LATENT = 2, B200_MIXER_MLSTM = 3 } b200_mixer_kind;
+ * weight to the expert's INPUT, be ungated (down(act(up x))), and come with one shared expert of the same shape.
+ *
+ * Third layer form (b200_stack_cfg.form = B200_FORM_POSTNORM): the norm follows the sum,
+ *   x = LN(residual_alpha * x + mixer(x)),   x = LN'(residual_alpha * x + ff(x))      (the second line only with a feed-forward),
+ * LN a layer norm with weight and bias; both sublayers read the stream itself.  The output is LN_final(x) times the head.
+ * Mixers of this form: B200_MIXER_ATTENTION with B200_MIXF_HEAD_NORM (q and k RMS-normalised per head with one weight of
+ * `dim` entries), B200_MIXF_VALUE_IS_KEY (no value projection: the value of a token is its key projection before norm and
+ * rotation, leading vdim entries) and B200_MIXF_SINK_ONE (one more unit in the softmax denominator);  B200_MIXER_LATENT
+ * with q_rank > 0 (queries through a normed latent of their own: q = W_uq rms(W_dq h)), B200_MIXF_HEAD_GATE (one sigmoid
+ * gate per head) and kv_share (the layer caches nothing and reads another layer's latent rows);  any attention mixer with
+ * `window` > 0 sees only the last `window` positions, its own included;  and
+ *
+ * B200_MIXER_DELTA: delta-rule recurrence with one decay per head and key channel.  q, k (kv_heads x dim) and v (heads x vdim)
+ * pass a causal per-channel convolution of `conv_taps` taps and silu; q and k become unit vectors per head (q times
+ * dim^-1/2); beta = sigmoid(w_b . h) per head; decay = exp(-exp(a_log[head]) softplus(W_a2 (W_a1 h) + dt_bias)) per head and
+ * key channel; per head  S = diag(decay) S;  u = beta (v - S^T k);  S += k u^T;  o = S^T q;  o is brought to unit RMS per
+ * head, times a weight, times sigmoid(W_g2 (W_g1 h)).  S (fp32) and the last conv_taps - 1 inputs of the convolution live
+ * in the sequence's state slot. */
+typedef enum b200_mixer_kind { B200_MIXER_ATTENTION = 1, B200_MIXER_LATENT = 2, B200_MIXER_MLSTM = 3, B200_MIXER_DELTA = 4 } b200_mixer_kind;
 typedef enum b200_mlp_kind { B200_MLP_NONE = 0, B200_MLP_MOE = 1, B200_MLP_DENSE = 2 } b200_mlp_kind;
-typedef enum b200_act_kind { B200_ACT_SILU = 0, B200_ACT_GELU_TANH = 1, B200_ACT_RELU2 = 2 } b200_act_kind;
-typedef enum b200_stack_form { B200_FORM_SANDWICH = 0, B200_FORM_PARALLEL = 1 } b200_stack_form;
-enum { B200_MIXF_SINK = 1, B200_MIXF_GATE = 2 };
+typedef enum b200_act_kind { B200_ACT_SILU = 0, B200_ACT_GELU_TANH = 1, B200_ACT_RELU2 = 2, B200_ACT_RELU = 3 } b200_act_kind;
+typedef enum b200_stack_form { B200_FORM_SANDWICH = 0, B200_FORM_PARALLEL = 1, B200_FORM_POSTNORM = 2 } b200_stack_form;
+enum { B200_MIXF_SINK = 1, B200_MIXF_GATE = 2, B200_MIXF_HEAD_NORM = 4, B200_MIXF_VALUE_IS_KEY = 8, B200_MIXF_SINK_ONE = 16,
+       B200_MIXF_HEAD_GATE = 32 };
 
 typedef struct b200_stack_layer {
   int32_t mixer;                       /* b200_mixer_kind */
@@ -415,6 +433,11 @@ typedef struct b200_stack_layer {
   int32_t sigmoid_scores;              /* router scores are sigmoids of the logits (no softmax) */
   int32_t weight_input;                /* the mixing weight multiplies the expert's input instead of its output */
   int32_t shared_ff;                   /* intermediate size of the shared expert (0: none) */
+  int32_t window;                      /* attention mixers: positions a query sees, its own included (0: all) */
+  int32_t q_rank;                      /* latent mixer: size of the query latent (0: queries straight from the fused projection) */
+  int32_t kv_share;                    /* latent mixer: 1 + the layer whose cached latent rows this layer reads (0: its own) */
+  int32_t conv_taps;                   /* delta mixer: taps of the q/k/v convolution (>= 1) */
+  int32_t decay_rank, gate_rank;       /* delta mixer: inner sizes of the two-step decay and output-gate projections */
 } b200_stack_layer;
 
 typedef struct b200_stack_cfg {
@@ -431,6 +454,7 @@ typedef struct b200_stack_cfg {
   int32_t bigram_buckets, bigram_mul_prev, bigram_mul_cur;   /* buckets > 0: hashed bigram rows are added to the embedding */
   float logit_softcap;                 /* > 0: logits = cap * tanh(logits / cap) */
   int32_t n_state_slots;               /* per-sequence state slots (previous token, convolution tails, recurrent state) */
+  float residual_alpha;                /* post-norm form: the stream's factor inside the norm */
 } b200_stack_cfg;
 
 typedef enum b200_stack_weight {
@@ -463,7 +487,22 @@ typedef enum b200_stack_weight {
   B200_SW_MLP_GATE_UP = 24, /* bf16 [2*ff][width]: gate rows, then up rows */
   B200_SW_MLP_DOWN = 25,    /* bf16 [width][ff] */
   B200_SW_SHARED_UP = 26,   /* bf16 [shared_ff][width] */
-  B200_SW_SHARED_DOWN = 27  /* bf16 [width][shared_ff] */
+  B200_SW_SHARED_DOWN = 27, /* bf16 [width][shared_ff] */
+  /* post-norm form: NORM_MIX_POST / NORM_MLP_POST / FINAL_NORM are the weights [width] of the norms after the two sums and of
+     the output; their biases follow.  QKV is the fused projection of the stream: attention (values = keys) [heads*dim +
+     kv_heads*dim][width]; latent [q_rank + (kv_rank unless shared) + heads][width] (query latent, key/value latent, gate rows);
+     delta: q | k | v | a1 | g1 | b rows, each of the last three groups starting at a multiple of 8 rows (zero rows between),
+     the total a multiple of 8 (b200_delta_fused_rows).  Q_NORM / K_NORM of a head-norm attention are [dim]. */
+  B200_SW_NORM_MIX_POST_BIAS = 28, /* f32 [width] */
+  B200_SW_NORM_MLP_POST_BIAS = 29, /* f32 [width] */
+  B200_SW_FINAL_NORM_BIAS = 30,    /* f32 [width] */
+  B200_SW_Q_LATENT_NORM = 31,      /* f32 [q_rank] */
+  B200_SW_UQ = 32,                 /* bf16 [heads*dim][q_rank] */
+  B200_SW_CONV = 33,               /* f32  [2*kv_heads*dim + heads*vdim][conv_taps]: q, k, v channels; the last tap is the current token's */
+  B200_SW_DECAY_UP = 34,           /* bf16 [heads*dim][decay_rank] */
+  B200_SW_DECAY_BIAS = 35,         /* f32  [heads*dim] */
+  B200_SW_DECAY_LOG = 36,          /* f32  [heads] */
+  B200_SW_GATE_UP = 37             /* bf16 [heads*vdim][gate_rank] */
 } b200_stack_weight;
 
 B200_API int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_layer* layers, b200_ctx** out);
@@ -487,6 +526,9 @@ B200_API int b200_stack_set_stream_tap(b200_ctx* ctx, float* out);
 B200_API int64_t b200_stack_state_bytes(b200_ctx* ctx);
 B200_API int b200_stack_set_state(b200_ctx* ctx, void* state);
 B200_API int b200_stack_set_step_slots(b200_ctx* ctx, const int32_t* seq_slots, int32_t n_seqs);
+/* Rows of the delta mixer's fused projection and where its groups start: offsets[0..5] = q, k, v, a1, g1, b. */
+B200_API int32_t b200_delta_fused_rows(int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim, int32_t decay_rank, int32_t gate_rank,
+                                       int32_t* offsets);
 /* The logit rows of the LAST step as fp32 [n_rows][vocab] into host memory (asynchronously: synchronise the stream before
  * reading).  With f32 they are the unrounded logits; otherwise the bf16 logits widened.  Works for every ctx on one GPU. */
 B200_API int b200_ctx_logits_last_f32(b200_ctx* ctx, int32_t n_rows, float* host_out, void* stream);
@@ -608,6 +650,54 @@ B200_API int64_t b200_moe_workspace_bytes(int32_t n_tokens, int32_t top, int32_t
 B200_API int b200_moe_experts(int32_t f32, const void* x, const void* w_gate_up, const void* w_down, const int32_t* ids,
                      const float* weights, int32_t n_tokens, int32_t width, int32_t ff, int32_t experts, int32_t top, float* parts,
                      void* workspace, void* stream);
+/* ---- per-kernel entry points of the post-norm form (unit tests, profiling); f32 as above ---- */
+/* x[r] = LN(alpha * x_in[rows ? rows[r] : r] + y[r]) * w + b over fp32 rows (y optional, of the activation type); x_out fp32
+ * and / or out_act (activation type) receive the result; x_out may be x_in when rows is NULL. */
+B200_API int b200_postnorm_stream(int32_t f32, const float* x_in, const void* y, float alpha, const float* w, const float* b, float* x_out,
+                                  void* out_act, const int32_t* rows, int32_t n_rows, int32_t width, float eps, void* stream);
+/* Fused rows [heads*dim q | kv_heads*dim k] of leading dimension ld: values = the raw key rows' leading vdim entries into v_cache;
+ * q and k RMS-normalised per head with qw / kw [dim], the leading rot_dims dimensions turned in neighbouring pairs by
+ * table rot [max_pos][2][rot_dims/2]; q_out fp32 [T][heads*dim], k into k_cache; caches [block][kv_heads][block_size][dim | vdim]. */
+B200_API int b200_qk_headnorm_rotate_cache(int32_t f32, const void* qk, int64_t ld, const float* qw, const float* kw, const int32_t* positions,
+                                           const int32_t* slot_mapping, const float* rot, int32_t rot_dims, int64_t max_pos, float* q_out,
+                                           void* k_cache, void* v_cache, int32_t n_tokens, int32_t heads, int32_t kv_heads, int32_t dim,
+                                           int32_t vdim, int32_t block_size, float eps, void* stream);
+/* b200_paged_attn_anydim_ex with a window: row t sees the last `window` keys of its context only (0: all). */
+B200_API int b200_paged_attn_window(int32_t f32, const float* q, const void* k_cache, const void* v_cache, const int32_t* block_table,
+                                    int32_t bt_stride, const int32_t* row_to_seq, const int32_t* ctx_lens, const int32_t* positions,
+                                    void* out, int32_t n_tokens, int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim,
+                                    int32_t block_size, float scale, int32_t shared_tiles, void* workspace, int32_t k_row, int32_t v_row,
+                                    const float* sink, int32_t window, void* stream);
+/* b200_latent_attn with a window (n_splits 1). */
+B200_API int b200_latent_attn_window(const float* q, const void* cache, const int32_t* block_table, int32_t bt_stride,
+                                     const int32_t* row_to_seq, const int32_t* ctx_lens, void* out, int32_t n_tokens, int32_t heads,
+                                     int32_t k_row, int32_t rank, int32_t block_size, float scale, const float* sink, void* workspace,
+                                     int32_t window, void* stream);
+/* Fused rows [q_rank | kv_rank ...] of leading dimension ld: cq[t] = rms(row[:q_rank]) * qw (activation type, rows of q_rank);
+ * cache row at slot_mapping[t] = rms(row[q_rank : q_rank + kv_rank]) * kw (skipped when cache is NULL). */
+B200_API int b200_latent_norms(int32_t f32, const void* fused, int64_t ld, int32_t q_rank, int32_t kv_rank, const float* qw, const float* kw,
+                               const int32_t* slot_mapping, void* cq, void* cache, int32_t n_tokens, float eps, void* stream);
+/* b200_head_linear whose gate is one number per head (gate[t * ldg + h]). */
+B200_API int b200_head_linear_head_gate(int32_t f32, const void* x, int64_t ldx, int32_t x_hs, const void* w, void* y, int64_t ldy,
+                                        int32_t y_hs, const void* gate, int64_t ldg, int32_t n_tokens, int32_t heads, int32_t n_out,
+                                        int32_t k, void* stream);
+/* Delta mixer, after the projections.  fused [T][ld] (groups at the offsets of b200_delta_fused_rows), a2 [T][heads*dim] =
+ * W_a2 a1 (activation type).  prep: convolution (tails [slot][taps-1][C] fp32, slot_stride floats apart; a portion that
+ * starts at position 0 sees zeros) + silu, unit q (times dim^-1/2) and k, beta, decay -> fp32 qn, kn [T][kv_heads*dim],
+ * vn [T][heads*vdim], beta [T][heads], decay [T][heads*dim].  tails: the last taps-1 raw q|k|v rows of every sequence go into
+ * its slot (after prep).  scan: the recurrence over state [slot][heads][vdim][dim] fp32, out fp32 [T][heads*vdim]. */
+B200_API int b200_delta_prep(int32_t f32, const void* fused, int64_t ld, const void* a2, const float* conv_w, const float* dt_bias,
+                             const float* a_log, const int32_t* positions, const int32_t* row_to_seq, const int32_t* seq_start,
+                             const int32_t* seq_slots, const float* tails, int64_t slot_stride, float* qn, float* kn, float* vn,
+                             float* beta, float* decay, int32_t n_tokens, int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim,
+                             int32_t taps, int32_t decay_rank, int32_t gate_rank, void* stream);
+B200_API int b200_delta_tails(int32_t f32, const void* fused, int64_t ld, const int32_t* positions, const int32_t* seq_start,
+                              const int32_t* seq_slots, float* tails, int64_t slot_stride, int32_t n_seqs, int32_t channels, int32_t taps,
+                              void* stream);
+B200_API int b200_delta_scan(const float* qn, const float* kn, const float* vn, const float* beta, const float* decay,
+                             const int32_t* positions, const int32_t* seq_start, const int32_t* seq_slots, float* state,
+                             int64_t slot_stride, float* out, int32_t n_seqs, int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim,
+                             void* stream);
 /* y[T][n_out] = x[T][k] . w[n_out][k]^T on CUDA cores in true fp32; w bf16, x / y fp32 or bf16. */
 B200_API int b200_linear_simt(int32_t x_f32, int32_t y_f32, const void* x, int64_t ldx, const void* w, void* y, int64_t ldy,
                      int32_t n_tokens, int32_t n_out, int32_t k, void* stream);
