@@ -647,6 +647,46 @@ def _dupolorn_config(Cf, name, z):
                              bigram_mul_prev=8191, bigram_mul_cur=127, logit_softcap=30.0, layers=layers)
 
 
+# Futidra beside Dupolorn (the closest model of the framework: latent attention over one cached row per token, a matrix-memory
+# recurrence with per-sequence state slots, dense feed-forwards) at equal width, layers, heads, head sizes, latent size and
+# feed-forward width.  Futidra's layers cycle latent attention, the delta rule (no feed-forward), attention whose values are its
+# keys, and latent attention reading the first layer's latents; Dupolorn's cycle latent attention, mLSTM, latent attention with
+# sink and gate, all with dense feed-forwards here.
+FUTIDRA_SIZES = {
+    "w2048": dict(width=2048, heads=16, dim=128, vdim=128, kv_rank=512, q_rank=768, kv=4, r_heads=16, r_dim=128, r_vdim=128, conv=4,
+                  rank=128, window=1024, ff=4096, layers=4, vocab=32768, rot_dim=64),
+    "w1024": dict(width=1024, heads=16, dim=64, vdim=64, kv_rank=256, q_rank=384, kv=4, r_heads=8, r_dim=128, r_vdim=128, conv=4,
+                  rank=64, window=512, ff=2048, layers=4, vocab=32768, rot_dim=32),
+}
+
+
+def _futidra_config(Cf, name, z):
+    rot = Cf.RotarySpec(base=500000.0, dims=z["dim"], factor=8.0, original=8192, fast=4.0, slow=1.0, scaled=True, kind="bands")
+    la = dict(heads=z["heads"], dim=z["dim"], rot_dim=0, vdim=z["vdim"], kv_rank=z["kv_rank"], scale=z["dim"] ** -0.5, q_rank=z["q_rank"],
+              window=z["window"], head_gate=True)
+    ff = Cf.FeedForwardSpec(kind="dense", ff=z["ff"], act="relu")
+    mixers = [(Cf.LatentAttentionSpec(**la), ff),
+              (Cf.ChannelDeltaSpec(heads=z["r_heads"], kv_heads=z["r_heads"], dim=z["r_dim"], vdim=z["r_vdim"], conv=z["conv"],
+                                   decay_rank=z["rank"], gate_rank=z["rank"]), None),
+              (Cf.AttentionSpec(heads=z["heads"], kv_heads=z["kv"], dim=z["dim"], vdim=z["dim"], scale=z["dim"] ** -0.5, rot=rot,
+                                window=z["window"], head_norm=True, value_is_key=True, sink_one=True), ff),
+              (Cf.LatentAttentionSpec(kv_from=0, **la), ff)]
+    layers = [Cf.StackLayerSpec(mixer=mixers[i % 4][0], mlp=mixers[i % 4][1]) for i in range(z["layers"])]
+    return Cf.FutidraConfig(name=name, width=z["width"], vocab=z["vocab"], postln_alpha=2.0, layers=layers)
+
+
+def _dupolorn_dense_config(Cf, name, z):
+    rot = Cf.RotarySpec(base=10000.0, dims=z["rot_dim"])
+    la = dict(heads=z["heads"], dim=z["dim"], rot_dim=z["rot_dim"], vdim=z["vdim"], kv_rank=z["kv_rank"],
+              scale=(z["dim"] + z["rot_dim"]) ** -0.5, rot=rot)
+    mixers = [Cf.LatentAttentionSpec(**la), Cf.MLSTMSpec(heads=z["r_heads"], dim=z["r_dim"], vdim=z["r_vdim"], gate_cap=15.0),
+              Cf.LatentAttentionSpec(sink=True, gate=True, **la)]
+    dense = Cf.FeedForwardSpec(kind="dense", ff=z["ff"], act="gelu_tanh")
+    layers = [Cf.ParallelLayerSpec(mixer=mixers[i % 3], mlp=dense) for i in range(z["layers"])]
+    return Cf.DupolornConfig(name=name, width=z["width"], vocab=z["vocab"], embed_scale=1.0, canon_taps=4, bigram_buckets=0,
+                             logit_softcap=0.0, layers=layers)
+
+
 def _design_batch(R, n_seqs, ctx, n_new, bs, vocab):
     """n_seqs sequences that already hold ctx tokens and bring n_new rows each; the last row of each is a logit row."""
     import numpy as np
@@ -696,18 +736,22 @@ def run_design(args):
     sampler.start()
     t0 = time.monotonic()
     out = []
-    dup = args.design == "dupolorn"
-    sizes = DUPOLORN_SIZES if dup else DESIGN_SIZES
+    dup, fut = args.design == "dupolorn", args.design == "futidra"
+    sizes = FUTIDRA_SIZES if fut else (DUPOLORN_SIZES if dup else DESIGN_SIZES)
     names = [n for n in sizes if args.design_size in ("all", n)]
     for name in names:
         z = sizes[name]
+        if fut:
+            z = dict(z, experts=1, top=1, groups=1, keep=1)
         rot = Cf.RotarySpec(base=10000.0, dims=z["dim"], factor=4.0, original=4096, fast=32.0, slow=1.0, scaled=True)
         att = Cf.AttentionSpec(heads=z["heads"], kv_heads=z["kv"], dim=z["dim"], vdim=z["dim"], scale=z["dim"] ** -0.5, rot=rot,
                                value_rot=Cf.RotarySpec(base=10000.0, dims=z["dim"]))
         moe = Cf.MoESpec(experts=z["experts"], top=z["top"], ff=z["ff"], groups=z["groups"], keep=z["keep"])
         arms = {"bopilorn": Cf.BopilornConfig(name=name, width=z["width"], vocab=z["vocab"], embed_scale=1.0,
                                               layers=[Cf.StackLayerSpec(mixer=att, mlp=moe) for _ in range(z["layers"])])}
-        if dup:
+        if fut:
+            arms = {"futidra": _futidra_config(Cf, name, z), "dupolorn": _dupolorn_dense_config(Cf, name, z)}
+        elif dup:
             arms = {"dupolorn": _dupolorn_config(Cf, name, z), "bopilorn": arms["bopilorn"]}
         elif z["dim"] == 128:
             arms["llama"] = Cf.ModelConfig(name=name, hidden=z["width"], n_layers=z["layers"], n_q_heads=z["heads"], n_kv_heads=z["kv"],
@@ -733,8 +777,9 @@ def run_design(args):
             torch.cuda.empty_cache()
         out.append(rec)
     clocks = sampler.stop(t0, time.monotonic())
-    emit({"metric": "design_compare", "design": "Dupolorn" if dup else "Bopilorn",
-          "closest": "bopilorn (layer-list model with routed experts)" if dup else "llama (fixed decoder stack)", "dtype": "bf16",
+    emit({"metric": "design_compare", "design": "Futidra" if fut else ("Dupolorn" if dup else "Bopilorn"),
+          "closest": "dupolorn with dense feed-forwards (latent attention, matrix-memory recurrence, state slots)" if fut else
+                     ("bopilorn (layer-list model with routed experts)" if dup else "llama (fixed decoder stack)"), "dtype": "bf16",
           "data": "synthetic, random-init weights", "steps": K, "warmup": W, "l2": "flushed between steps (512 MiB written)",
           "sizes": out, "clocks": clocks})
 
@@ -748,10 +793,10 @@ def main():
     ap.add_argument("--workload", default="llama8b-bs64", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--headline-only", action="store_true", help="skip the `also` and `tp` sections of the default run")
-    ap.add_argument("--design", default=None, choices=["bopilorn", "dupolorn"],
+    ap.add_argument("--design", default=None, choices=["bopilorn", "dupolorn", "futidra"],
                     help="instead of the default workload: prefill / decode throughput of this design beside the closest fixed-stack "
                          "model at equal size")
-    ap.add_argument("--design-size", default="all", choices=["all"] + sorted(set(DESIGN_SIZES) | set(DUPOLORN_SIZES)))
+    ap.add_argument("--design-size", default="all", choices=["all"] + sorted(set(DESIGN_SIZES) | set(DUPOLORN_SIZES) | set(FUTIDRA_SIZES)))
     args = ap.parse_args()
     claim_stdout()
     if args.design:

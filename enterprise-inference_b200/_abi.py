@@ -159,6 +159,9 @@ SIGNATURES = {
     "b200_paged_attn_window": (C.c_int, [_i32, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _f32,
                                          _i32, _vp, _i32, _i32, _vp, _i32, _vp]),
     "b200_latent_attn_window": (C.c_int, [_vp, _vp, _vp, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _f32, _vp, _vp, _i32, _vp]),
+    "b200_paged_attn_mma_supported": (C.c_int, [_i32, _i32, _i32, _i32]),
+    "b200_paged_attn_mma": (C.c_int, [_vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _vp, _vp, _i32, _i32,
+                                      _vp, _vp]),
     "b200_latent_norms": (C.c_int, [_i32, _vp, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _f32, _vp]),
     "b200_head_linear_head_gate": (C.c_int, [_i32, _vp, _i64, _i32, _vp, _vp, _i64, _i32, _vp, _i64, _i32, _i32, _i32, _i32, _vp]),
     "b200_delta_prep": (C.c_int, [_i32, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _i32, _i32,

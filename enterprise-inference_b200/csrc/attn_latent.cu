@@ -12,6 +12,9 @@
 // Steps with few (row, head) pairs and long contexts split the context over several CTAs per pair group (n_splits): each
 // leaves unnormalised sums with its maximum and denominator, a merge kernel combines them.
 //
+// The same kernel serves grouped-query attention with a value cache of its own (paged_attn_mma): the pairs of a CTA are then
+// (row, head) pairs of ONE kv head's group, the key tile [64][dim] and the value tile [64][vdim] are gathered side by side.
+//
 // Queries come as fp32 rows [T][heads][krow] (rounded to bf16 when staged); output rows are bf16 [T][heads][rank].
 // Shapes: krow and rank multiples of 16, rank <= 512.  Everything else (and the 32-bit mode) takes attn_anydim.cu; both walk
 // the same cache and the same run list, and agree within bf16 rounding of the operands.
@@ -50,7 +53,8 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 
 template <int NG>   // 16-column output groups per warp: rank <= 128 NG
 __global__ void __launch_bounds__(kLaThreads)
-latent_attn_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __restrict__ kc, const int32_t* __restrict__ block_table,
+latent_attn_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
+                       int kv_heads, const int32_t* __restrict__ block_table,
                        int bt_stride, const int32_t* __restrict__ row_to_seq, const int32_t* __restrict__ ctx_lens,
                        __nv_bfloat16* __restrict__ out, const int32_t* __restrict__ runs, const int32_t* __restrict__ n_runs, int heads,
                        int krow, int rank, int block_size, float scale, const float* __restrict__ sink, int n_splits,
@@ -58,14 +62,19 @@ latent_attn_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __restr
   extern __shared__ __align__(16) unsigned char smraw[];
   pdl_wait();
   pdl_launch_dependents();
-  const int item = blockIdx.x, chunk = blockIdx.y;
+  // G query heads share kv head g; a pair i of the group is (row t0 + i / G, head g G + i % G).  Latent rows: one kv head, G = heads.
+  const int G = heads / kv_heads;
+  const int item = blockIdx.x, chunk = blockIdx.y % G, g = blockIdx.y / G;
   if (item >= *n_runs) return;
   const int t0 = runs[2 * item], nr = runs[2 * item + 1];
-  const int nq = nr * heads, i0 = chunk * kLaPairs;
+  const int nq = nr * G, i0 = chunk * kLaPairs;
   if (i0 >= nq) return;
   const int ks = krow + 8;   // bf16 elements per staged row: 16-byte aligned, 4 words off a bank multiple
+  // a value cache of its own (vc) is staged beside the keys in rows of rank + 8; else a key row's leading entries are its value
+  const int vs = vc ? rank + 8 : ks;
   __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smraw);      // [64][ks]
-  __nv_bfloat16* Qs = Ks + kLaKeys * ks;                            // [16][ks]
+  __nv_bfloat16* Vs = vc ? Ks + kLaKeys * ks : Ks;                  // [64][vs]
+  __nv_bfloat16* Qs = Vs + (vc ? kLaKeys * vs : kLaKeys * ks);      // [16][ks]
   float* Ss = reinterpret_cast<float*>(Qs + kLaPairs * ks);         // [16][68]
   __nv_bfloat16* Ps = reinterpret_cast<__nv_bfloat16*>(Ss + kLaPairs * kSsStride);   // [16][72]
   float* corr = reinterpret_cast<float*>(Ps + kLaPairs * kPsStride);                 // [16]
@@ -76,29 +85,29 @@ latent_attn_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __restr
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid < kLaPairs) {
     const int i = i0 + tid;
-    ctxp[tid] = i < nq ? ctx_lens[t0 + i / heads] : 0;
+    ctxp[tid] = i < nq ? ctx_lens[t0 + i / G] : 0;
     lop[tid] = window > 0 ? max(ctxp[tid] - window, 0) : 0;
     mrow[tid] = -INFINITY;
     lrow[tid] = 0.f;
   }
   for (int e = tid; e < kLaPairs * krow; e += kLaThreads) {
     const int p = e / krow, d = e % krow, i = i0 + p;
-    Qs[p * ks + d] = __float2bfloat16_rn(i < nq ? q[((int64_t)(t0 + i / heads) * heads + i % heads) * krow + d] : 0.f);
+    Qs[p * ks + d] = __float2bfloat16_rn(i < nq ? q[((int64_t)(t0 + i / G) * heads + g * G + i % G) * krow + d] : 0.f);
   }
-  const int last_row = min(nr - 1, (i0 + kLaPairs - 1) / heads);
+  const int last_row = min(nr - 1, (i0 + kLaPairs - 1) / G);
   const int ctx_max = ctx_lens[t0 + last_row];
   const int32_t* bt = block_table + (int64_t)(row_to_seq ? row_to_seq[t0] : t0) * bt_stride;
-  const int cpr = krow >> 3;   // 16-byte chunks per row
+  const int cpr = krow >> 3, cpv = rank >> 3;   // 16-byte chunks per key / value row
   float o[NG][8];
 #pragma unroll
-  for (int g = 0; g < NG; ++g)
+  for (int cg = 0; cg < NG; ++cg)
 #pragma unroll
-    for (int j = 0; j < 8; ++j) o[g][j] = 0.f;
+    for (int j = 0; j < 8; ++j) o[cg][j] = 0.f;
   __syncthreads();
 
   // with n_splits > 1 this CTA walks only its share of the tiles and leaves unnormalised sums for the merge kernel
   // (with a window the walk starts at the tile that holds the oldest key the group's first row sees)
-  const int tile0 = window > 0 ? max(ctx_lens[t0 + i0 / heads] - window, 0) / kLaKeys : 0;
+  const int tile0 = window > 0 ? max(ctx_lens[t0 + i0 / G] - window, 0) / kLaKeys : 0;
   const int tiles = (ctx_max + kLaKeys - 1) / kLaKeys - tile0, per = (tiles + n_splits - 1) / n_splits;
   const int base_lo = (tile0 + blockIdx.z * per) * kLaKeys, base_hi = min(ctx_max, (tile0 + (int)(blockIdx.z + 1) * per) * kLaKeys);
   for (int base = base_lo; base < base_hi; base += kLaKeys) {
@@ -107,13 +116,21 @@ latent_attn_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __restr
       // four threads per key row, alternate 16-byte chunks: one block-table lookup per thread and tile
       const int r = tid >> 2;
       __nv_bfloat16* dst = Ks + r * ks;
+      __nv_bfloat16* dstv = Vs + r * vs;
       if (r < n) {
         const int j = base + r;
-        const __nv_bfloat16* src = kc + ((int64_t)bt[j / block_size] * block_size + j % block_size) * krow;
+        const int64_t crow = ((int64_t)bt[j / block_size] * kv_heads + g) * block_size + j % block_size;
+        const __nv_bfloat16* src = kc + crow * krow;
         for (int c = tid & 3; c < cpr; c += 4) cp_async16(dst + c * 8, src + c * 8);
+        if (vc) {
+          const __nv_bfloat16* srcv = vc + crow * rank;
+          for (int c = tid & 3; c < cpv; c += 4) cp_async16(dstv + c * 8, srcv + c * 8);
+        }
       } else {
         // rows past the context: finite values under zero weights
         for (int c = tid & 3; c < cpr; c += 4) *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+        if (vc)
+          for (int c = tid & 3; c < cpv; c += 4) *reinterpret_cast<uint4*>(dstv + c * 8) = make_uint4(0u, 0u, 0u, 0u);
       }
     }
     cp_async_wait_all();
@@ -168,24 +185,24 @@ latent_attn_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __restr
     {
       const float c_lo = corr[lane >> 2], c_hi = corr[(lane >> 2) + 8];
 #pragma unroll
-      for (int g = 0; g < NG; ++g) {
-        o[g][0] *= c_lo; o[g][1] *= c_lo; o[g][4] *= c_lo; o[g][5] *= c_lo;
-        o[g][2] *= c_hi; o[g][3] *= c_hi; o[g][6] *= c_hi; o[g][7] *= c_hi;
+      for (int cg = 0; cg < NG; ++cg) {
+        o[cg][0] *= c_lo; o[cg][1] *= c_lo; o[cg][4] *= c_lo; o[cg][5] *= c_lo;
+        o[cg][2] *= c_hi; o[cg][3] *= c_hi; o[cg][6] *= c_hi; o[cg][7] *= c_hi;
       }
       const __nv_bfloat16* ap = Ps + (lane & 15) * kPsStride + (lane >> 4) * 8;
-      const __nv_bfloat16* vp = Ks + ((lane & 7) + ((lane >> 3) & 1) * 8) * ks + (lane >> 4) * 8;
+      const __nv_bfloat16* vp = Vs + ((lane & 7) + ((lane >> 3) & 1) * 8) * vs + (lane >> 4) * 8;
 #pragma unroll
       for (int kk = 0; kk < kLaKeys / 16; ++kk) {
         uint32_t a[4];
         ldsm_x4(a, ap + kk * 16);
 #pragma unroll
-        for (int g = 0; g < NG; ++g) {
-          const int col0 = (warp + kLaWarps * g) * 16;
+        for (int cg = 0; cg < NG; ++cg) {
+          const int col0 = (warp + kLaWarps * cg) * 16;
           if (col0 < rank) {
             uint32_t b[4];
-            ldsm_x4_t(b, vp + kk * 16 * ks + col0);
-            mma_bf16(o[g][0], o[g][1], o[g][2], o[g][3], a, b[0], b[1]);
-            mma_bf16(o[g][4], o[g][5], o[g][6], o[g][7], a, b[2], b[3]);
+            ldsm_x4_t(b, vp + kk * 16 * vs + col0);
+            mma_bf16(o[cg][0], o[cg][1], o[cg][2], o[cg][3], a, b[0], b[1]);
+            mma_bf16(o[cg][4], o[cg][5], o[cg][6], o[cg][7], a, b[2], b[3]);
           }
         }
       }
@@ -197,7 +214,7 @@ latent_attn_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __restr
     const int prow = rank + 2;
     if (tid < kLaPairs && i0 + tid < nq) {
       const int i = i0 + tid;
-      float* dst = part + (((int64_t)(t0 + i / heads) * heads + i % heads) * n_splits + blockIdx.z) * prow;
+      float* dst = part + (((int64_t)(t0 + i / G) * heads + g * G + i % G) * n_splits + blockIdx.z) * prow;
       dst[rank] = mrow[tid];
       dst[rank + 1] = lrow[tid];
     }
@@ -205,16 +222,16 @@ latent_attn_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __restr
     for (int half = 0; half < 2; ++half) {
       const int p = (lane >> 2) + half * 8, i = i0 + p;
       if (i >= nq) continue;
-      float* dst = part + (((int64_t)(t0 + i / heads) * heads + i % heads) * n_splits + blockIdx.z) * prow;
+      float* dst = part + (((int64_t)(t0 + i / G) * heads + g * G + i % G) * n_splits + blockIdx.z) * prow;
 #pragma unroll
-      for (int g = 0; g < NG; ++g) {
-        const int col0 = (warp + kLaWarps * g) * 16;
+      for (int cg = 0; cg < NG; ++cg) {
+        const int col0 = (warp + kLaWarps * cg) * 16;
         if (col0 < rank) {
 #pragma unroll
           for (int nt = 0; nt < 2; ++nt) {
             const int col = col0 + nt * 8 + (lane & 3) * 2;
-            dst[col] = o[g][nt * 4 + half * 2];
-            dst[col + 1] = o[g][nt * 4 + half * 2 + 1];
+            dst[col] = o[cg][nt * 4 + half * 2];
+            dst[col + 1] = o[cg][nt * 4 + half * 2 + 1];
           }
         }
       }
@@ -226,7 +243,7 @@ latent_attn_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __restr
   for (int half = 0; half < 2; ++half) {
     const int p = (lane >> 2) + half * 8, i = i0 + p;
     if (i >= nq) continue;
-    const int t = t0 + i / heads, h = i % heads;
+    const int t = t0 + i / G, h = g * G + i % G;
     float l = lrow[p], osc = 1.f;
     if (sink != nullptr) {
       const float m = mrow[p], sk = sink[h], mn = fmaxf(m, sk);
@@ -236,14 +253,14 @@ latent_attn_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __restr
     const float inv = l > 0.f ? osc / l : 0.f;
     __nv_bfloat16* dst = out + ((int64_t)t * heads + h) * rank;
 #pragma unroll
-    for (int g = 0; g < NG; ++g) {
-      const int col0 = (warp + kLaWarps * g) * 16;
+    for (int cg = 0; cg < NG; ++cg) {
+      const int col0 = (warp + kLaWarps * cg) * 16;
       if (col0 < rank) {
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
           const int col = col0 + nt * 8 + (lane & 3) * 2;
           *reinterpret_cast<__nv_bfloat162*>(dst + col) =
-              __floats2bfloat162_rn(o[g][nt * 4 + half * 2] * inv, o[g][nt * 4 + half * 2 + 1] * inv);
+              __floats2bfloat162_rn(o[cg][nt * 4 + half * 2] * inv, o[cg][nt * 4 + half * 2 + 1] * inv);
         }
       }
     }
@@ -299,29 +316,40 @@ int latent_attn_splits(int T, int heads, int rank, int max_ctx, int64_t ws_bytes
   return std::max(n, 1);
 }
 
-bool latent_attn_mma_supported(int heads, int krow, int rank) {
-  static const int env = getenv("B200_LATENT_MMA") ? atoi(getenv("B200_LATENT_MMA")) : 1;
-  const size_t smem = (size_t)(kLaKeys + kLaPairs) * (krow + 8) * 2 + kLaPairs * (kSsStride * 4 + kPsStride * 2 + 20);
-  return env && heads > 0 && krow % 16 == 0 && rank % 16 == 0 && rank > 0 && rank <= 512 && rank <= krow && smem <= 200 * 1024;
+static size_t la_smem(int krow, int rank, bool own_values) {
+  return (size_t)(kLaKeys + kLaPairs) * (krow + 8) * 2 + (own_values ? (size_t)kLaKeys * (rank + 8) * 2 : 0) +
+         kLaPairs * (kSsStride * 4 + kPsStride * 2 + 20);
 }
 
-// runs / n_runs: the run list of the step (attn_anydim.cu builds it: runs of at most 16 consecutive rows of one sequence)
-int latent_attn_mma(const float* q, const __nv_bfloat16* kc, const int32_t* block_table, int bt_stride, const int32_t* row_to_seq,
-                    const int32_t* ctx_lens, __nv_bfloat16* out, const int32_t* runs, const int32_t* n_runs, int T, int heads, int krow,
-                    int rank, int block_size, float scale, const float* sink, cudaStream_t s, int n_splits, float* part, int window) {
-  if (T == 0) return B200_OK;
+bool latent_attn_mma_supported(int heads, int krow, int rank) {
+  static const int env = getenv("B200_LATENT_MMA") ? atoi(getenv("B200_LATENT_MMA")) : 1;
+  return env && heads > 0 && krow % 16 == 0 && rank % 16 == 0 && rank > 0 && rank <= 512 && rank <= krow && la_smem(krow, rank, false) <= 200 * 1024;
+}
+
+// grouped-query attention with a value cache of its own on the same kernel: key rows of `dim`, value rows of `vdim` entries
+bool paged_attn_mma_supported(int heads, int kv_heads, int dim, int vdim) {
+  static const int env = getenv("B200_ATTN_MMA") ? atoi(getenv("B200_ATTN_MMA")) : 1;
+  return env && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dim % 16 == 0 && vdim % 16 == 0 && vdim > 0 && vdim <= 512 &&
+         la_smem(dim, vdim, true) <= 200 * 1024;
+}
+
+static int attn_mma_launch(const float* q, const __nv_bfloat16* kc, const __nv_bfloat16* vc, int kv_heads, const int32_t* block_table,
+                           int bt_stride, const int32_t* row_to_seq, const int32_t* ctx_lens, __nv_bfloat16* out, const int32_t* runs,
+                           const int32_t* n_runs, int T, int heads, int krow, int rank, int block_size, float scale, const float* sink,
+                           cudaStream_t s, int n_splits, float* part, int window) {
   if (n_splits < 1 || part == nullptr) n_splits = 1;
-  B200_REQUIRE(n_splits <= kLaMaxSplits, B200_ERR_INVALID, "latent_attn_mma: %d splits (at most %d)", n_splits, kLaMaxSplits);
-  B200_REQUIRE(latent_attn_mma_supported(heads, krow, rank), B200_ERR_UNSUPPORTED, "latent_attn_mma: shape %d / %d / %d", heads, krow, rank);
-  B200_REQUIRE(reinterpret_cast<uintptr_t>(kc) % 16 == 0, B200_ERR_INVALID, "latent_attn_mma: cache not 16-byte aligned");
-  const size_t smem = (size_t)(kLaKeys + kLaPairs) * (krow + 8) * 2 + kLaPairs * (kSsStride * 4 + kPsStride * 2 + 20);
-  const dim3 grid(T, (16 * heads + kLaPairs - 1) / kLaPairs, n_splits), block(kLaThreads);
+  B200_REQUIRE(n_splits <= kLaMaxSplits, B200_ERR_INVALID, "attention: %d splits (at most %d)", n_splits, kLaMaxSplits);
+  B200_REQUIRE(reinterpret_cast<uintptr_t>(kc) % 16 == 0 && reinterpret_cast<uintptr_t>(vc) % 16 == 0, B200_ERR_INVALID,
+               "attention: cache not 16-byte aligned");
+  const size_t smem = la_smem(krow, rank, vc != nullptr);
+  // a run has at most 16 rows, so a kv head's group has at most 16 G pairs: G chunks of 16
+  const dim3 grid(T, heads, n_splits), block(kLaThreads);
 #define LA(NGV)                                                                                                                     \
   do {                                                                                                                              \
     static bool done[64] = {};                                                                                                      \
     if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(latent_attn_mma_kernel<NGV>, 200 * 1024, done));                            \
-    B200_CUDA(launch(latent_attn_mma_kernel<NGV>, grid, block, smem, s, q, kc, block_table, bt_stride, row_to_seq, ctx_lens, out, runs, \
-                     n_runs, heads, krow, rank, block_size, scale, sink, n_splits, part, window));                                          \
+    B200_CUDA(launch(latent_attn_mma_kernel<NGV>, grid, block, smem, s, q, kc, vc, kv_heads, block_table, bt_stride, row_to_seq, ctx_lens, \
+                     out, runs, n_runs, heads, krow, rank, block_size, scale, sink, n_splits, part, window));                       \
   } while (0)
   if (rank <= 128) LA(1);
   else if (rank <= 256) LA(2);
@@ -331,6 +359,28 @@ int latent_attn_mma(const float* q, const __nv_bfloat16* kc, const int32_t* bloc
     B200_CUDA(launch(latent_attn_merge_kernel, dim3((T * heads + 3) / 4), dim3(128), (size_t)0, s, (const float*)part, out, T * heads, heads,
                      rank, n_splits, sink));
   return B200_OK;
+}
+
+// runs / n_runs: the run list of the step (attn_anydim.cu builds it: runs of at most 16 consecutive rows of one sequence)
+int latent_attn_mma(const float* q, const __nv_bfloat16* kc, const int32_t* block_table, int bt_stride, const int32_t* row_to_seq,
+                    const int32_t* ctx_lens, __nv_bfloat16* out, const int32_t* runs, const int32_t* n_runs, int T, int heads, int krow,
+                    int rank, int block_size, float scale, const float* sink, cudaStream_t s, int n_splits, float* part, int window) {
+  if (T == 0) return B200_OK;
+  B200_REQUIRE(latent_attn_mma_supported(heads, krow, rank), B200_ERR_UNSUPPORTED, "latent_attn_mma: shape %d / %d / %d", heads, krow, rank);
+  return attn_mma_launch(q, kc, nullptr, 1, block_table, bt_stride, row_to_seq, ctx_lens, out, runs, n_runs, T, heads, krow, rank, block_size,
+                         scale, sink, s, n_splits, part, window);
+}
+
+// caches [block][kv_heads][block_size][dim | vdim] bf16, fp32 queries [T][heads][dim], bf16 output [T][heads][vdim]
+int paged_attn_mma(const float* q, const __nv_bfloat16* kc, const __nv_bfloat16* vc, const int32_t* block_table, int bt_stride,
+                   const int32_t* row_to_seq, const int32_t* ctx_lens, __nv_bfloat16* out, const int32_t* runs, const int32_t* n_runs, int T,
+                   int heads, int kv_heads, int dim, int vdim, int block_size, float scale, const float* sink, cudaStream_t s, int n_splits,
+                   float* part, int window) {
+  if (T == 0) return B200_OK;
+  B200_REQUIRE(vc && paged_attn_mma_supported(heads, kv_heads, dim, vdim), B200_ERR_UNSUPPORTED, "paged_attn_mma: shape %d / %d / %d / %d", heads,
+               kv_heads, dim, vdim);
+  return attn_mma_launch(q, kc, vc, kv_heads, block_table, bt_stride, row_to_seq, ctx_lens, out, runs, n_runs, T, heads, dim, vdim, block_size,
+                         scale, sink, s, n_splits, part, window);
 }
 
 }  // namespace b200

@@ -307,6 +307,12 @@ int latent_attn_mma(const float* q, const __nv_bfloat16* kc, const int32_t* bloc
                     const int32_t* ctx_lens, __nv_bfloat16* out, const int32_t* runs, const int32_t* n_runs, int T, int heads, int krow,
                     int rank, int block_size, float scale, const float* sink, cudaStream_t s, int n_splits = 1, float* part = nullptr,
                     int window = 0);
+// the same kernel for grouped-query attention over key and value caches [block][kv_heads][block_size][dim | vdim]
+bool paged_attn_mma_supported(int heads, int kv_heads, int dim, int vdim);
+int paged_attn_mma(const float* q, const __nv_bfloat16* kc, const __nv_bfloat16* vc, const int32_t* block_table, int bt_stride,
+                   const int32_t* row_to_seq, const int32_t* ctx_lens, __nv_bfloat16* out, const int32_t* runs, const int32_t* n_runs, int T,
+                   int heads, int kv_heads, int dim, int vdim, int block_size, float scale, const float* sink, cudaStream_t s,
+                   int n_splits = 1, float* part = nullptr, int window = 0);
 // context splits for a step (1: none); part holds T * heads * n_splits * (rank + 2) floats
 int latent_attn_splits(int T, int heads, int rank, int max_ctx, int64_t ws_bytes);
 // mixture of experts (moe.cu)

@@ -315,10 +315,21 @@ static int stack_enqueue_step_postnorm(b200_ctx* c, const StepArgs& a, cudaStrea
       STEP(qk_headnorm_rotate_cache(f32, M->qkv, qr, W.q_norm, W.k_norm, a.positions, a.slots, rot, L.rot_dims, max_pos, M->q, W.kc, W.vc, T,
                                     L.heads, L.kv_heads, L.dim, L.vdim, m.block_size, m.norm_eps, s));
       const float* sink = (L.mixer_flags & B200_MIXF_SINK_ONE) ? M->zero_sink : nullptr;
+      if (!f32 && paged_attn_mma_supported(L.heads, L.kv_heads, L.dim, L.vdim)) {
+        if (attn_plan != 2 && !runs_built) STEP(paged_attn_runs_plan(a.row_to_seq, a.ctx_lens, T, M->attn_ws, s));
+        runs_built = true;
+        if (attn_plan == 1) attn_plan = 2;
+        const int seen = L.window > 0 ? std::min(a.max_ctx, L.window + 64) : a.max_ctx;
+        STEP(paged_attn_mma(M->q, (const __nv_bfloat16*)W.kc, (const __nv_bfloat16*)W.vc, a.block_table, a.bt_stride, a.row_to_seq, a.ctx_lens,
+                            (__nv_bfloat16*)M->attn, static_cast<const int32_t*>(M->attn_ws) + 8, static_cast<const int32_t*>(M->attn_ws), T,
+                            L.heads, L.kv_heads, L.dim, L.vdim, m.block_size, L.scale, sink, s,
+                            latent_attn_splits(T, L.heads, L.vdim, seen, M->lat_ws_bytes), M->lat_ws, L.window));
+      } else {
       STEP(paged_attn_anydim(f32, M->q, W.kc, W.vc, a.block_table, a.bt_stride, a.row_to_seq, a.ctx_lens, a.positions, nullptr, max_pos,
                              M->attn, T, L.heads, L.kv_heads, L.dim, L.vdim, m.block_size, L.scale, runs_built && attn_plan == 1 ? 2 : attn_plan,
                              M->attn_ws, s, 0, 0, sink, L.window));
       if (attn_plan == 1) attn_plan = 2, runs_built = true;
+      }
     } else if (is_latent(L)) {
       const int kr = L.kv_rank, hd = L.heads * L.dim;
       void* cache = L.kv_share > 0 ? M->w[L.kv_share - 1].kc : W.kc;
@@ -804,6 +815,10 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
       if (is_latent(layers[l]) && latent_attn_mma_supported(layers[l].heads, layers[l].kv_rank + layers[l].rot_dim, layers[l].kv_rank))
         // splitting only happens below one CTA per SM: at most 148 * 16 pairs, 16 splits
         M->lat_ws_bytes = std::max<int64_t>(M->lat_ws_bytes, std::min<int64_t>(T * layers[l].heads, 148 * 16) * 16 * (layers[l].kv_rank + 2) * 4);
+  if (post && !cfg->f32)
+    for (int l = 0; l < cfg->n_layers; ++l)
+      if (layers[l].mixer == B200_MIXER_ATTENTION && paged_attn_mma_supported(layers[l].heads, layers[l].kv_heads, layers[l].dim, layers[l].vdim))
+        M->lat_ws_bytes = std::max<int64_t>(M->lat_ws_bytes, std::min<int64_t>(T * layers[l].heads, 148 * 16) * 16 * (layers[l].vdim + 2) * 4);
   struct Item {
     void** p;
     int64_t bytes;
@@ -1359,4 +1374,21 @@ extern "C" int b200_delta_scan(const float* qn, const float* kn, const float* vn
   B200_REQUIRE(qn && kn && vn && beta && decay && out, B200_ERR_INVALID, "delta_scan: null argument");
   return delta_scan(qn, kn, vn, beta, decay, positions, seq_start, seq_slots, state, slot_stride, out, S, heads, kv_heads, dim, vdim,
                     (cudaStream_t)stream);
+}
+
+extern "C" int b200_paged_attn_mma_supported(int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim) {
+  return paged_attn_mma_supported(heads, kv_heads, dim, vdim) ? 1 : 0;
+}
+
+extern "C" int b200_paged_attn_mma(const float* q, const void* kc, const void* vc, const int32_t* block_table, int32_t bt_stride,
+                                   const int32_t* row_to_seq, const int32_t* ctx_lens, void* out, int32_t T, int32_t heads, int32_t kv_heads,
+                                   int32_t dim, int32_t vdim, int32_t block_size, float scale, const float* sink, void* workspace, int32_t window,
+                                   int32_t n_splits, float* part, void* stream) {
+  B200_REQUIRE(q && kc && vc && block_table && ctx_lens && out && workspace && block_size > 0 && window >= 0, B200_ERR_INVALID,
+               "paged_attn_mma: bad argument");
+  int rc = paged_attn_runs_plan(row_to_seq, ctx_lens, T, workspace, (cudaStream_t)stream);
+  if (rc) return rc;
+  return paged_attn_mma(q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, block_table, bt_stride, row_to_seq, ctx_lens, (__nv_bfloat16*)out,
+                        static_cast<const int32_t*>(workspace) + 8, static_cast<const int32_t*>(workspace), T, heads, kv_heads, dim, vdim,
+                        block_size, scale, sink, (cudaStream_t)stream, n_splits, part, window);
 }

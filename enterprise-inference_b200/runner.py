@@ -599,6 +599,60 @@ class StackRunner(ModelRunner):
                     self._set(i, A.SW_SHARED_UP, rnd(f.shared_ff, c.width))
                     self._set(i, A.SW_SHARED_DOWN, rnd(c.width, f.shared_ff))
 
+    def _init_random_postnorm(self, seed: int, std: float):
+        from .config import AttentionSpec, ChannelDeltaSpec
+        from .weights import delta_fused_offsets
+        c, A = self.cfg, _abi
+        g = torch.Generator(device=self.device)
+        g.manual_seed(seed)
+
+        def rnd(*shape, sd=std):
+            t = torch.empty(shape, dtype=torch.bfloat16, device=self.device)
+            t.normal_(0.0, sd, generator=g)
+            return t
+
+        ones, zeros = torch.ones(c.width, device=self.device), torch.zeros(c.width, device=self.device)
+        emb = rnd(c.vocab, c.width, sd=1.0)
+        self._set(0, A.SW_EMBED, emb)
+        self._set(0, A.SW_HEAD, emb)
+        self._set(0, A.SW_FINAL_NORM, ones)
+        self._set(0, A.SW_FINAL_NORM_BIAS, zeros)
+        for i, L in enumerate(c.layers):
+            a, f = L.mixer, L.mlp
+            self._set(i, A.SW_NORM_MIX_POST, ones)
+            self._set(i, A.SW_NORM_MIX_POST_BIAS, zeros)
+            if isinstance(a, AttentionSpec):
+                self._set(i, A.SW_QKV, rnd((a.heads + a.kv_heads) * a.dim, c.width))
+                self._set(i, A.SW_Q_NORM, torch.ones(a.dim, device=self.device))
+                self._set(i, A.SW_K_NORM, torch.ones(a.dim, device=self.device))
+            elif isinstance(a, ChannelDeltaSpec):
+                rows, off = delta_fused_offsets(a)
+                fused = rnd(rows, c.width)
+                for lo, n in zip(off, (a.kv_heads * a.dim, a.kv_heads * a.dim, a.heads * a.vdim, a.decay_rank, a.gate_rank, a.heads)):
+                    fused[lo + n:(off[off.index(lo) + 1] if lo != off[-1] else rows)] = 0
+                self._set(i, A.SW_QKV, fused)
+                self._set(i, A.SW_CONV, rnd(2 * a.kv_heads * a.dim + a.heads * a.vdim, a.conv, sd=0.5).float())
+                self._set(i, A.SW_DECAY_UP, rnd(a.heads * a.dim, a.decay_rank))
+                self._set(i, A.SW_DECAY_BIAS, torch.zeros(a.heads * a.dim, device=self.device))
+                self._set(i, A.SW_DECAY_LOG, torch.zeros(a.heads, device=self.device))
+                self._set(i, A.SW_GATE_UP, rnd(a.heads * a.vdim, a.gate_rank))
+                self._set(i, A.SW_HEAD_NORM, torch.ones(a.heads * a.vdim, device=self.device))
+            else:
+                own = a.kv_from is None
+                self._set(i, A.SW_QKV, rnd(a.q_rank + (a.kv_rank if own else 0) + a.heads, c.width))
+                self._set(i, A.SW_Q_LATENT_NORM, torch.ones(a.q_rank, device=self.device))
+                self._set(i, A.SW_UQ, rnd(a.heads * a.dim, a.q_rank, sd=a.q_rank ** -0.5))
+                if own:
+                    self._set(i, A.SW_K_NORM, torch.ones(a.kv_rank, device=self.device))
+                self._set(i, A.SW_UK_T, rnd(a.heads * a.kv_rank, a.dim, sd=a.kv_rank ** -0.5))
+                self._set(i, A.SW_UV, rnd(a.heads * a.vdim, a.kv_rank, sd=a.kv_rank ** -0.5))
+            self._set(i, A.SW_O, rnd(c.width, a.heads * a.vdim))
+            if f is not None:
+                self._set(i, A.SW_NORM_MLP_POST, ones)
+                self._set(i, A.SW_NORM_MLP_POST_BIAS, zeros)
+                self._set(i, A.SW_MLP_GATE_UP, rnd(2 * f.ff, c.width))
+                self._set(i, A.SW_MLP_DOWN, rnd(c.width, f.ff))
+
     def set_step_slots(self, seq_slots: Optional[torch.Tensor]):
         """Device-pointer steps (step_device) of a model with state slots: int32 device tensor, one slot per sequence of the step."""
         self._step_slots = seq_slots
@@ -608,6 +662,8 @@ class StackRunner(ModelRunner):
         """Random-init weights generated on the device (benchmarks).  Norm weights are 1, the router bias 0."""
         if self.parallel:
             return self._init_random_parallel(seed, std)
+        if self.postnorm:
+            return self._init_random_postnorm(seed, std)
         c, A = self.cfg, _abi
         g = torch.Generator(device=self.device)
         g.manual_seed(seed)

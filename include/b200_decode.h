@@ -673,6 +673,14 @@ B200_API int b200_latent_attn_window(const float* q, const void* cache, const in
                                      const int32_t* row_to_seq, const int32_t* ctx_lens, void* out, int32_t n_tokens, int32_t heads,
                                      int32_t k_row, int32_t rank, int32_t block_size, float scale, const float* sink, void* workspace,
                                      int32_t window, void* stream);
+/* Grouped-query attention over bf16 key and value caches [block][kv_heads][block_size][dim | vdim] on the tensor cores (dim and
+ * vdim multiples of 16, vdim <= 512: b200_paged_attn_mma_supported): fp32 queries [T][heads][dim], bf16 output [T][heads][vdim],
+ * optional sink [heads] and window; n_splits > 1 with part (n_tokens * heads * n_splits * (vdim + 2) floats) splits the context. */
+B200_API int b200_paged_attn_mma_supported(int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim);
+B200_API int b200_paged_attn_mma(const float* q, const void* k_cache, const void* v_cache, const int32_t* block_table, int32_t bt_stride,
+                                 const int32_t* row_to_seq, const int32_t* ctx_lens, void* out, int32_t n_tokens, int32_t heads,
+                                 int32_t kv_heads, int32_t dim, int32_t vdim, int32_t block_size, float scale, const float* sink,
+                                 void* workspace, int32_t window, int32_t n_splits, float* part, void* stream);
 /* Fused rows [q_rank | kv_rank ...] of leading dimension ld: cq[t] = rms(row[:q_rank]) * qw (activation type, rows of q_rank);
  * cache row at slot_mapping[t] = rms(row[q_rank : q_rank + kv_rank]) * kw (skipped when cache is NULL). */
 B200_API int b200_latent_norms(int32_t f32, const void* fused, int64_t ld, int32_t q_rank, int32_t kv_rank, const float* qw, const float* kw,

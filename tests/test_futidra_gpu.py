@@ -212,6 +212,37 @@ def test_windowed_latent_attention_on_the_tensor_cores(window, bs, heads):
         assert float((_attend(q, k, k, queries, window + 1, scale, False) - want).abs().max()) > 0.05
 
 
+@pytest.mark.parametrize("splits", [1, 3])
+@pytest.mark.parametrize("window,bs,heads,kv_heads,dim,vdim", [(1, 16, 4, 2, 32, 32), (63, 16, 6, 2, 48, 32), (64, 64, 4, 4, 64, 64), (65, 128, 8, 2, 128, 128),
+                                                               (200, 64, 5, 1, 16, 16), (1000, 16, 2, 1, 160, 144)])
+def test_windowed_grouped_attention_on_the_tensor_cores(splits, window, bs, heads, kv_heads, dim, vdim):
+    """Key and value caches of their own, query heads grouped over kv heads, the extra unit in the denominator, windows around
+    the 64-key tile, the context split over CTAs and merged."""
+    n, scale = 300, 0.3
+    queries = list(range(255, 300)) + [min(window, 299), 63, 64, 128]
+    q, k, v = _spiked(n, heads, kv_heads, dim, vdim, queries, window, window + heads)
+    want = _attend(q, k, v, queries, window, scale, True)
+    nb = (n + bs - 1) // bs
+    order = torch.randperm(nb + 2, generator=torch.Generator().manual_seed(3)).tolist()
+    kc, vc = _paged(k, bs, nb + 2, order, torch.bfloat16), _paged(v, bs, nb + 2, order, torch.bfloat16)
+    T = len(queries)
+    bt = i32([order[:nb]] * 5)
+    rts = [0] * 45 + [1, 2, 3, 4]
+    ctx = [p + 1 for p in queries]
+    assert lib().b200_paged_attn_mma_supported(heads, kv_heads, dim, vdim)
+    out = torch.zeros(T, heads * vdim, dtype=torch.bfloat16, device=DEV)
+    ws = torch.zeros(lib().b200_paged_attn_anydim_workspace_bytes(T), dtype=torch.uint8, device=DEV)
+    part = torch.zeros(T * heads * splits * (vdim + 2), device=DEV)
+    check(lib().b200_paged_attn_mma(dev(q.reshape(T, -1)).data_ptr(), kc.data_ptr(), vc.data_ptr(), bt.data_ptr(), nb, i32(rts).data_ptr(),
+                                    i32(ctx).data_ptr(), out.data_ptr(), T, heads, kv_heads, dim, vdim, bs, scale, dev(torch.zeros(heads)).data_ptr(),
+                                    ws.data_ptr(), window, splits, part.data_ptr(), None))
+    sync()
+    got = out.float().cpu().double().reshape(T, heads, vdim)
+    assert torch.allclose(got, want, atol=3e-2, rtol=3e-2)
+    if window < 250:
+        assert float((_attend(q, k, v, queries, window + 1, scale, True) - want).abs().max()) > 0.05
+
+
 @pytest.mark.parametrize("f32", [1, 0])
 def test_latent_norms_and_the_gate_of_one_number_per_head(f32):
     g = torch.Generator().manual_seed(8)
