@@ -8,9 +8,9 @@
 //   S_t   = diag(g_t) S_{t-1};   u = b_t (v_t - S_t^T k_t);   S_t += k_t u^T;   o_t = S_t^T q_t
 // Head h reads q/k head h / (heads / kv_heads).
 //
-//  * delta_prep: one CTA per row: convolution taps from the step's own rows or, before the portion's first row, from the
+//  * delta_prep: two CTAs per row (one for beta and the decays): convolution taps from the step's own rows or, before the portion's first row, from the
 //    slot's tail; silu; the unit vectors; beta; the decays.  Everything leaves in fp32.
-//  * delta_tails: one CTA per sequence, after prep: the last taps - 1 raw rows of the portion (or what is left of the old tail
+//  * delta_tails: CTAs of 256 channels per sequence, after prep: the last taps - 1 raw rows of the portion (or what is left of the old tail
 //    when the portion is shorter) become the slot's tail.
 //  * delta_scan: the recurrence.  The columns of S do not interact, so one CTA takes (sequence, head, 32 value columns); a warp
 //    owns 4 columns, a lane the key channels lane, lane + 32, ...; the state lives in registers during the walk and is
@@ -44,9 +44,18 @@ delta_prep_kernel(const AT* __restrict__ fused, int64_t ld, const AT* __restrict
   pdl_wait();
   pdl_launch_dependents();
   const int64_t t = blockIdx.x;
+  const int qk = kv_heads * dim, C = 2 * qk + heads * vdim;
+  if (blockIdx.y == 1) {   // the second CTA of a row: beta and the decays (nothing of the convolution enters them)
+    const int hd = heads * dim;
+    for (int h = threadIdx.x; h < heads; h += kPrepThreads) beta[t * heads + h] = sigmoid_f(ldx<AT>(fused, t * ld + off_b + h));
+    for (int c = threadIdx.x; c < hd; c += kPrepThreads) {
+      const float z = ldx<AT>(a2, t * hd + c) + dt_bias[c];
+      decay[t * hd + c] = expf(-expf(a_log[c / dim]) * softplus_f(z));
+    }
+    return;
+  }
   const int s = row_to_seq ? row_to_seq[t] : (int)t;
   const int start = seq_start[s], r = (int)t - start, pos = positions[t];
-  const int qk = kv_heads * dim, C = 2 * qk + heads * vdim;
   const float* tail = tails ? tails + (int64_t)seq_slots[s] * slot_stride : nullptr;   // [taps - 1][C]
   for (int c = threadIdx.x; c < C; c += kPrepThreads) {
     float a = 0.f;
@@ -69,13 +78,8 @@ delta_prep_kernel(const AT* __restrict__ fused, int64_t ld, const AT* __restrict
     float* dst = v < kv_heads ? qn + t * qk + (int64_t)v * dim : kn + t * qk + (int64_t)(v - kv_heads) * dim;
     for (int d = lane; d < dim; d += 32) dst[d] = src[d] * inv;
   }
-  const int hv = heads * vdim, hd = heads * dim;
+  const int hv = heads * vdim;
   for (int c = threadIdx.x; c < hv; c += kPrepThreads) vn[t * hv + c] = xs[2 * qk + c];
-  for (int h = threadIdx.x; h < heads; h += kPrepThreads) beta[t * heads + h] = sigmoid_f(ldx<AT>(fused, t * ld + off_b + h));
-  for (int c = threadIdx.x; c < hd; c += kPrepThreads) {
-    const float z = ldx<AT>(a2, t * hd + c) + dt_bias[c];
-    decay[t * hd + c] = expf(-expf(a_log[c / dim]) * softplus_f(z));
-  }
 }
 
 template <typename AT>
@@ -91,7 +95,8 @@ delta_tails_kernel(const AT* __restrict__ fused, int64_t ld, const int32_t* __re
   float* tail = tails + (int64_t)seq_slots[s] * slot_stride;
   // entry i holds the input of the position (taps - 2 - i) before the portion's last one.  A thread owns a channel and
   // walks i upwards: what it reads of the old tail lies above everything it has written.
-  for (int c = threadIdx.x; c < C; c += 256)
+  const int c = blockIdx.y * 256 + threadIdx.x;
+  if (c < C)
     for (int i = 0; i < taps - 1; ++i) {
       const int ri = n - taps + 1 + i;   // row of the portion, negative: before it
       float v;
@@ -127,12 +132,69 @@ delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
 #pragma unroll
     for (int c = 0; c < kDsCols; ++c) Sr[c][i] = (!fresh && d < dim && j0 + c < vd) ? S_st[((int64_t)h * vd + j0 + c) * dim + d] : 0.f;
   }
+  const int qk = kv_heads * dim, hd = heads * dim, hv = heads * vd;
+  if (n_rows == 1) {
+    // a decode row: nothing to stage; the row's inputs are fetched beside the state
+    const int64_t t = start;
+    const float b = beta[t * heads + h];
+    float dot[kDsCols], acc[kDsCols], v[kDsCols], q[DPL], k[DPL];
+#pragma unroll
+    for (int c = 0; c < kDsCols; ++c) {
+      dot[c] = 0.f;
+      acc[c] = 0.f;
+      v[c] = j0 + c < vd ? vn[t * hv + h * vd + j0 + c] : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) {
+      const int d = lane + 32 * i;
+      const bool live = d < dim;
+      q[i] = live ? qn[t * qk + g * dim + d] : 0.f;
+      k[i] = live ? kn[t * qk + g * dim + d] : 0.f;
+      const float gd = live ? decay[t * hd + h * dim + d] : 0.f;
+#pragma unroll
+      for (int c = 0; c < kDsCols; ++c) {
+        Sr[c][i] *= gd;
+        dot[c] = fmaf(Sr[c][i], k[i], dot[c]);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+      for (int c = 0; c < kDsCols; ++c) dot[c] += __shfl_xor_sync(0xffffffffu, dot[c], o);
+#pragma unroll
+    for (int c = 0; c < kDsCols; ++c) {
+      const float u = b * (v[c] - dot[c]);
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) {
+        Sr[c][i] = fmaf(k[i], u, Sr[c][i]);
+        acc[c] = fmaf(Sr[c][i], q[i], acc[c]);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+      for (int c = 0; c < kDsCols; ++c) acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], o);
+    float mine = 0.f;
+#pragma unroll
+    for (int c = 0; c < kDsCols; ++c)
+      if (lane == c) mine = acc[c];
+    if (lane < kDsCols && j0 + lane < vd) out[t * hv + h * vd + j0 + lane] = mine;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) {
+      const int d = lane + 32 * i;
+      if (d < dim) {
+#pragma unroll
+        for (int c = 0; c < kDsCols; ++c)
+          if (j0 + c < vd) S_st[((int64_t)h * vd + j0 + c) * dim + d] = Sr[c][i];
+      }
+    }
+    return;
+  }
   float* sq = stage;                       // [kDsStage][dim]
   float* sk = sq + kDsStage * dim;
   float* sg = sk + kDsStage * dim;
   float* sv = sg + kDsStage * dim;         // [kDsStage][32]
   float* sb = sv + kDsStage * kDsBlockCols;   // [kDsStage]
-  const int qk = kv_heads * dim, hd = heads * dim, hv = heads * vd;
   constexpr int EQ = 2 * DPL, EV = kDsStage * kDsBlockCols / kDsThreads;   // elements per thread of a [16][dim] / [16][32] tile
   float rq[EQ], rk[EQ], rg[EQ], rv[EV], rb = 0.f;
   auto prefetch = [&](int b0) {
@@ -266,12 +328,12 @@ int delta_prep(bool f32, const void* fused, int64_t ld, const void* a2, const fl
   static bool done[2][64] = {};
   if (f32) {
     if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(delta_prep_kernel<float>, 200 * 1024, done[0]));
-    B200_CUDA(launch(delta_prep_kernel<float>, dim3(T), dim3(kPrepThreads), smem, s, (const float*)fused, ld, (const float*)a2, conv_w, dt_bias,
+    B200_CUDA(launch(delta_prep_kernel<float>, dim3(T, 2), dim3(kPrepThreads), smem, s, (const float*)fused, ld, (const float*)a2, conv_w, dt_bias,
                      a_log, positions, row_to_seq, seq_start, seq_slots, tails, slot_stride, qn, kn, vn, beta, decay, heads, kv_heads, dim, vdim,
                      taps, off[5]));
   } else {
     if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(delta_prep_kernel<__nv_bfloat16>, 200 * 1024, done[1]));
-    B200_CUDA(launch(delta_prep_kernel<__nv_bfloat16>, dim3(T), dim3(kPrepThreads), smem, s, (const __nv_bfloat16*)fused, ld,
+    B200_CUDA(launch(delta_prep_kernel<__nv_bfloat16>, dim3(T, 2), dim3(kPrepThreads), smem, s, (const __nv_bfloat16*)fused, ld,
                      (const __nv_bfloat16*)a2, conv_w, dt_bias, a_log, positions, row_to_seq, seq_start, seq_slots, tails, slot_stride, qn, kn,
                      vn, beta, decay, heads, kv_heads, dim, vdim, taps, off[5]));
   }
@@ -283,10 +345,10 @@ int delta_tails(bool f32, const void* fused, int64_t ld, const int32_t* position
   if (S == 0 || taps <= 1) return B200_OK;
   B200_REQUIRE(tails && seq_slots && seq_start && positions, B200_ERR_INVALID, "delta_tails: null argument");
   if (f32)
-    B200_CUDA(launch(delta_tails_kernel<float>, dim3(S), dim3(256), (size_t)0, s, (const float*)fused, ld, positions, seq_start, seq_slots, tails,
+    B200_CUDA(launch(delta_tails_kernel<float>, dim3(S, (channels + 255) / 256), dim3(256), (size_t)0, s, (const float*)fused, ld, positions, seq_start, seq_slots, tails,
                      slot_stride, channels, taps));
   else
-    B200_CUDA(launch(delta_tails_kernel<__nv_bfloat16>, dim3(S), dim3(256), (size_t)0, s, (const __nv_bfloat16*)fused, ld, positions, seq_start,
+    B200_CUDA(launch(delta_tails_kernel<__nv_bfloat16>, dim3(S, (channels + 255) / 256), dim3(256), (size_t)0, s, (const __nv_bfloat16*)fused, ld, positions, seq_start,
                      seq_slots, tails, slot_stride, channels, taps));
   return B200_OK;
 }
