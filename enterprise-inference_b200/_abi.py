@@ -50,7 +50,7 @@ MIXF_SINK, MIXF_GATE, MIXF_HEAD_NORM, MIXF_VALUE_IS_KEY, MIXF_SINK_ONE, MIXF_HEA
  SW_K_NORM, SW_O, SW_ROUTER, SW_ROUTER_BIAS, SW_EXPERT_GATE_UP, SW_EXPERT_DOWN, SW_BIGRAM, SW_CANON, SW_DEPTH_AVG, SW_UK_T, SW_UV,
  SW_SINK, SW_GATES, SW_GATES_BIAS, SW_HEAD_NORM, SW_MLP_GATE_UP, SW_MLP_DOWN, SW_SHARED_UP, SW_SHARED_DOWN, SW_NORM_MIX_POST_BIAS,
  SW_NORM_MLP_POST_BIAS, SW_FINAL_NORM_BIAS, SW_Q_LATENT_NORM, SW_UQ, SW_CONV, SW_DECAY_UP, SW_DECAY_BIAS, SW_DECAY_LOG,
- SW_GATE_UP) = range(38)
+ SW_GATE_UP, SW_MLP_GATE_UP_INTERLEAVED) = range(39)
 SW_F32 = {SW_FINAL_NORM, SW_NORM_MIX_PRE, SW_NORM_MIX_POST, SW_NORM_MLP_PRE, SW_NORM_MLP_POST, SW_Q_NORM, SW_K_NORM, SW_ROUTER_BIAS,
           SW_CANON, SW_DEPTH_AVG, SW_SINK, SW_GATES_BIAS, SW_HEAD_NORM, SW_NORM_MIX_POST_BIAS, SW_NORM_MLP_POST_BIAS,
           SW_FINAL_NORM_BIAS, SW_Q_LATENT_NORM, SW_CONV, SW_DECAY_BIAS, SW_DECAY_LOG}

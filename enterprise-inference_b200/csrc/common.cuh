@@ -204,6 +204,7 @@ struct LinearExtra {
   __nv_bfloat16* vc = nullptr;
   int hq = 0, hkv = 0, block_size = 0;
   float* out_f32 = nullptr;
+  int act = 0;                   // mode 1: b200_act_kind of the gate (0: silu)
 };
 int linear_tc(const __nv_bfloat16* x, int64_t ldx, const __nv_bfloat16* w, const __nv_bfloat16* bias,
               __nv_bfloat16* y, int64_t ldy, int T, int n_out, int k, void* ws, int64_t ws_bytes,

@@ -187,6 +187,7 @@ struct TcParams {
   // grouped gate|up with the SiLU*mul epilogue: an expert's rows are [gate (gu_ff) | up (gu_ff)]; slab m of the launch is
   // gate rows m*64.. and the matching up rows, fetched as two 64-row boxes (the layout kSiluMul expects, made by TMA)
   int gu_ff;
+  int act;   // kSiluMul: b200_act_kind of the gate (0: silu, rounded to bf16 before the product as the fixed stack does)
   // kScatter: row t of the launch goes to grp_out[grp_pair[t]][n_out] (fp32, unrounded) times grp_wt[grp_pair[t]];
   // grp_pair[t] < 0 marks a padding row
   // (both null: the identity and weight 1, i.e. a plain fp32 output)
@@ -220,6 +221,7 @@ __device__ __forceinline__ void tc_trace(const TcParams& p, int slot) {
 //  kPlain    y[t][row] = bf16(acc + bias)
 //  kSiluMul  the slab holds 64 gate rows then the 64 matching up rows (B200_W_GATE_UP_INTERLEAVED):
 //            y[t][m_tile*64 + i] = bf16(bf16(silu(bf16(g_i))) * bf16(u_i))          (R5)
+//            (TcParams::act != 0: bf16(act(bf16(g_i)) * bf16(u_i)) for the other gate activations)
 //  kRopeKv   the slab is one head of the fused qkv projection: NeoX RoPE in bf16 arithmetic (R3) on q
 //            and k heads, q rows to y, k/v rows straight into the paged cache at slots[t]
 //  kResidual the linear's output is added to the fp32 residual stream (see TcParams::sres): no y is written
@@ -253,7 +255,7 @@ __device__ __forceinline__ void finalize4(const TcParams& p, int m_tile, int lan
     const float g0 = lo ? v[0] : x[2], g1 = lo ? v[1] : x[3];
     const float u0 = lo ? x[0] : v[2], u1 = lo ? x[1] : v[3];
     const int f = m_tile * 64 + (lane & 15) * 4 + (lo ? 0 : 2);                  // output feature
-    const float o0 = silu_to_bf16(g0) * u0, o1 = silu_to_bf16(g1) * u1;
+    const float o0 = (p.act == 0 ? silu_to_bf16(g0) : act_apply(g0, p.act)) * u0, o1 = (p.act == 0 ? silu_to_bf16(g1) : act_apply(g1, p.act)) * u1;
     __nv_bfloat16* dst = p.y + (int64_t)tok * p.ldy + f;
     if ((p.ldy % 2 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 3) == 0)) {
       *reinterpret_cast<uint32_t*>(dst) = pack_bf16(o0, o1);
@@ -1056,6 +1058,7 @@ int linear_tc(const __nv_bfloat16* x, int64_t ldx, const __nv_bfloat16* w, const
   p.trace = trace_buffer();
   if (mode == kSiluMul) {
     B200_REQUIRE(n_out % kBlockM == 0, B200_ERR_UNSUPPORTED, "linear_tc(silu_mul): n_out=%d must be a multiple of 128", n_out);
+    p.act = ex->act;
   } else if (mode == kRopeKv) {
     B200_REQUIRE(ex->positions && ex->slots && ex->cos_sin && ex->kc && ex->vc && ex->block_size > 0 &&
                      n_out == (ex->hq + 2 * ex->hkv) * kHeadDim,

@@ -54,6 +54,7 @@ struct StackLayerW {
   const float *n_mix_post_b = nullptr, *n_mlp_post_b = nullptr, *q_lat_norm = nullptr, *conv = nullptr, *decay_bias = nullptr,
               *decay_log = nullptr;
   const __nv_bfloat16 *uq = nullptr, *decay_up = nullptr, *gate_up = nullptr;
+  bool gu_interleaved = false;   // mlp_gate_up holds 128-row slabs of 64 gate rows + the 64 matching up rows
 };
 
 struct StackModel {
@@ -149,6 +150,25 @@ static int stack_linear(b200_ctx* c, const void* x, int64_t ldx, const __nv_bflo
     return linear_tc((const __nv_bfloat16*)x, ldx, w, nullptr, (__nv_bfloat16*)y, ldy, T, n_out, k, c->lin_ws, c->lin_ws_bytes,
                      nullptr, s);
   return linear_simt(false, false, x, ldx, w, y, ldy, T, n_out, k, s);
+}
+
+// Dense gated feed-forward, first half: act(gate x) * (up x) -> out [T][ff].  Interleaved weights: one tcgen05 launch whose
+// epilogue activates and multiplies; else the plain linear and the activation kernel.
+static int stack_gate_up(b200_ctx* c, const void* x, const StackLayerW& W, const b200_stack_layer& L, void* gu, void* out, int T, cudaStream_t s) {
+  const StackModel* M = c->stack;
+  const int Wd = M->cfg.width;
+  if (W.gu_interleaved) {
+    B200_REQUIRE(!M->cfg.f32 && linear_tc_supported(T, 2 * L.ff, Wd) && linear_tc_workspace_bytes(T, 2 * L.ff, Wd) <= c->lin_ws_bytes &&
+                     reinterpret_cast<uintptr_t>(x) % 16 == 0,
+                 B200_ERR_UNSUPPORTED, "feed-forward: interleaved gate|up weights need the tcgen05 linear (T=%d ff=%d width=%d)", T, L.ff, Wd);
+    LinearExtra ex;
+    ex.mode = 1;
+    ex.act = L.act;
+    return linear_tc((const __nv_bfloat16*)x, Wd, W.mlp_gate_up, nullptr, (__nv_bfloat16*)out, L.ff, T, 2 * L.ff, Wd, c->lin_ws, c->lin_ws_bytes, &ex, s);
+  }
+  int rc = stack_linear(c, x, Wd, W.mlp_gate_up, gu, 2 * L.ff, T, 2 * L.ff, Wd, s);
+  if (rc) return rc;
+  return ff_act(M->cfg.f32 != 0, gu, out, T, L.ff, true, L.act, s);
 }
 
 static int stack_ready_parallel(const b200_ctx* c) {
@@ -374,8 +394,7 @@ static int stack_enqueue_step_postnorm(b200_ctx* c, const StepArgs& a, cudaStrea
     STEP(stack_linear(c, M->attn, av, W.o, M->y, Wd, T, Wd, av, s));
     STEP(postnorm_stream(f32, x, M->y, m.residual_alpha, W.n_mix_post, W.n_mix_post_b, x, hcopy, nullptr, T, Wd, m.norm_eps, s));
     if (L.mlp == B200_MLP_DENSE) {
-      STEP(stack_linear(c, hin, Wd, W.mlp_gate_up, M->gu, 2 * L.ff, T, 2 * L.ff, Wd, s));
-      STEP(ff_act(f32, M->gu, M->ffa, T, L.ff, true, L.act, s));
+      STEP(stack_gate_up(c, hin, W, L, M->gu, M->ffa, T, s));
       STEP(stack_linear(c, M->ffa, L.ff, W.mlp_down, M->y2, Wd, T, Wd, L.ff, s));
       STEP(postnorm_stream(f32, x, M->y2, m.residual_alpha, W.n_mlp_post, W.n_mlp_post_b, x, hcopy, nullptr, T, Wd, m.norm_eps, s));
     }
@@ -472,8 +491,7 @@ static int stack_enqueue_step_parallel(b200_ctx* c, const StepArgs& a, cudaStrea
     const float* parts = nullptr;
     int n_parts = 0;
     if (L.mlp == B200_MLP_DENSE) {
-      STEP(stack_linear(c, M->hn, Wd, W.mlp_gate_up, M->gu, 2 * L.ff, T, 2 * L.ff, Wd, s));
-      STEP(ff_act(f32, M->gu, M->ffa, T, L.ff, true, L.act, s));
+      STEP(stack_gate_up(c, M->hn, W, L, M->gu, M->ffa, T, s));
       STEP(stack_linear(c, M->ffa, L.ff, W.mlp_down, M->y2, Wd, T, Wd, L.ff, s));
       y_ff = M->y2;
     } else if (L.mlp == B200_MLP_MOE) {
@@ -935,14 +953,15 @@ extern "C" int b200_stack_set_weight(b200_ctx* c, int32_t layer, int32_t kind, c
     case B200_SW_GATES: er = 2 * (int64_t)L.heads; ec = Wd; break;
     case B200_SW_GATES_BIAS: er = 2 * (int64_t)L.heads; break;
     case B200_SW_HEAD_NORM: er = (int64_t)L.heads * L.vdim; break;
-    case B200_SW_MLP_GATE_UP: er = 2 * (int64_t)L.ff; ec = Wd; break;
+    case B200_SW_MLP_GATE_UP: case B200_SW_MLP_GATE_UP_INTERLEAVED: er = 2 * (int64_t)L.ff; ec = Wd; break;
     case B200_SW_MLP_DOWN: er = Wd; ec = L.ff; break;
     case B200_SW_SHARED_UP: er = (int64_t)(L.ungated ? 1 : 2) * L.shared_ff; ec = Wd; break;
     case B200_SW_SHARED_DOWN: er = Wd; ec = L.shared_ff; break;
     default: B200_REQUIRE(false, B200_ERR_INVALID, "stack_set_weight: unknown kind %d", kind);
   }
   B200_REQUIRE(kind < B200_SW_BIGRAM || par || post, B200_ERR_INVALID, "stack_set_weight: kind %d belongs to another layer form", kind);
-  B200_REQUIRE(kind < B200_SW_NORM_MIX_POST_BIAS || post, B200_ERR_INVALID, "stack_set_weight: kind %d belongs to the post-norm form", kind);
+  B200_REQUIRE(kind < B200_SW_NORM_MIX_POST_BIAS || post || kind == B200_SW_MLP_GATE_UP_INTERLEAVED, B200_ERR_INVALID,
+               "stack_set_weight: kind %d belongs to the post-norm form", kind);
   if (kind == B200_SW_Q_LATENT_NORM || kind == B200_SW_UQ)
     B200_REQUIRE(is_latent(L) && L.q_rank > 0, B200_ERR_INVALID, "stack_set_weight: layer %d has no query latent", layer);
   if (kind >= B200_SW_CONV && kind <= B200_SW_GATE_UP)
@@ -951,7 +970,10 @@ extern "C" int b200_stack_set_weight(b200_ctx* c, int32_t layer, int32_t kind, c
     B200_REQUIRE(is_latent(L), B200_ERR_INVALID, "stack_set_weight: layer %d has no latent attention", layer);
   if (kind == B200_SW_GATES || kind == B200_SW_GATES_BIAS || kind == B200_SW_HEAD_NORM)
     B200_REQUIRE(is_mlstm(L) || (is_delta(L) && kind == B200_SW_HEAD_NORM), B200_ERR_INVALID, "stack_set_weight: layer %d has no recurrence", layer);
-  if (kind == B200_SW_MLP_GATE_UP || kind == B200_SW_MLP_DOWN)
+  if (kind == B200_SW_MLP_GATE_UP_INTERLEAVED)
+    B200_REQUIRE(!M->cfg.f32 && L.ff % 64 == 0 && Wd % 8 == 0, B200_ERR_UNSUPPORTED,
+                 "stack_set_weight: interleaved gate|up rows need the bf16 mode, ff %% 64 == 0 and width %% 8 == 0");
+  if (kind == B200_SW_MLP_GATE_UP || kind == B200_SW_MLP_DOWN || kind == B200_SW_MLP_GATE_UP_INTERLEAVED)
     B200_REQUIRE(L.mlp == B200_MLP_DENSE, B200_ERR_INVALID, "stack_set_weight: layer %d has no dense feed-forward", layer);
   B200_REQUIRE(rows == er && cols == ec, B200_ERR_INVALID, "stack_set_weight: kind %d of layer %d expects [%lld,%lld], got [%lld,%lld]",
                kind, layer, (long long)er, (long long)ec, (long long)rows, (long long)cols);
@@ -985,7 +1007,8 @@ extern "C" int b200_stack_set_weight(b200_ctx* c, int32_t layer, int32_t kind, c
     case B200_SW_GATES: M->w[layer].gates = b; break;
     case B200_SW_GATES_BIAS: M->w[layer].gates_bias = f; break;
     case B200_SW_HEAD_NORM: M->w[layer].head_norm = f; break;
-    case B200_SW_MLP_GATE_UP: M->w[layer].mlp_gate_up = b; break;
+    case B200_SW_MLP_GATE_UP: M->w[layer].mlp_gate_up = b; M->w[layer].gu_interleaved = false; break;
+    case B200_SW_MLP_GATE_UP_INTERLEAVED: M->w[layer].mlp_gate_up = b; M->w[layer].gu_interleaved = true; break;
     case B200_SW_MLP_DOWN: M->w[layer].mlp_down = b; break;
     case B200_SW_SHARED_UP: M->w[layer].shared_up = b; break;
     case B200_SW_SHARED_DOWN: M->w[layer].shared_down = b; break;

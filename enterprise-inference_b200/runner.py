@@ -7,6 +7,8 @@ it owns the weights, the paged KV cache and the step inputs, and runs `execute_m
 """
 from __future__ import annotations
 
+import os
+
 import ctypes as C
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
@@ -438,6 +440,8 @@ class StackRunner(ModelRunner):
         from .config import AttentionSpec, ChannelDeltaSpec, DupolornConfig, FutidraConfig, MLSTMSpec
         self.parallel = isinstance(cfg, DupolornConfig)
         self.postnorm = isinstance(cfg, FutidraConfig)
+        # dense feed-forwards of the post-norm form in bf16: gate activation and product in the gate|up linear's epilogue
+        self.fuse_gate_up = self.postnorm and not self.f32 and os.environ.get("B200_STACK_FUSE_GATE_UP", "1") != "0"
         stateful = (self.parallel or self.postnorm) and cfg.needs_state
         self.n_state_slots = int(n_state_slots) if stateful else 0
         if stateful and self.n_state_slots <= 0:
@@ -535,7 +539,13 @@ class StackRunner(ModelRunner):
 
     def _set(self, layer: int, kind: int, t: torch.Tensor):
         dt = torch.float32 if kind in _abi.SW_F32 else torch.bfloat16
-        t = t.to(device=self.device, dtype=dt).contiguous()
+        t = t.to(device=self.device, dtype=dt)
+        if kind == _abi.SW_MLP_GATE_UP and self.fuse_gate_up and (t.shape[0] // 2) % 64 == 0 and t.shape[1] % 8 == 0:
+            # the tcgen05 linear activates and multiplies in its epilogue over slabs of 64 gate rows + the 64 matching up rows
+            from .weights import interleave_gate_up
+            ff = t.shape[0] // 2
+            t, kind = interleave_gate_up(t[:ff], t[ff:]), _abi.SW_MLP_GATE_UP_INTERLEAVED
+        t = t.contiguous()
         self._weights.append(t)
         rows, cols = (t.shape[0], t.shape[1]) if t.dim() == 2 else (t.shape[0], 1)
         _abi.check(self.lib.b200_stack_set_weight(self.ctx, layer, kind, t.data_ptr(), rows, cols))

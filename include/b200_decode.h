@@ -502,7 +502,10 @@ typedef enum b200_stack_weight {
   B200_SW_DECAY_UP = 34,           /* bf16 [heads*dim][decay_rank] */
   B200_SW_DECAY_BIAS = 35,         /* f32  [heads*dim] */
   B200_SW_DECAY_LOG = 36,          /* f32  [heads] */
-  B200_SW_GATE_UP = 37             /* bf16 [heads*vdim][gate_rank] */
+  B200_SW_GATE_UP = 37,            /* bf16 [heads*vdim][gate_rank] */
+  B200_SW_MLP_GATE_UP_INTERLEAVED = 38 /* bf16 [2*ff][width] in 128-row slabs: 64 gate rows, then the 64 matching up rows; this OR
+                                          B200_SW_MLP_GATE_UP.  bf16 mode, ff % 64 == 0, width % 8 == 0: the gate activation and the
+                                          product run in the linear's epilogue */
 } b200_stack_weight;
 
 B200_API int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_layer* layers, b200_ctx** out);

@@ -501,6 +501,29 @@ def test_bf16_mode_within_bf16_noise_and_equal_across_schedules(model_a):
     r.close()
 
 
+def test_gate_activation_in_the_linears_epilogue_equals_the_separate_kernel(monkeypatch):
+    """Feed-forward widths that are multiples of 64 take interleaved gate|up slabs and activate in the tcgen05 epilogue; relu of a
+    bf16 value is exact, so the logits equal those of the plain linear followed by the activation kernel bit for bit."""
+    cfg = F.make_cfg(width=128, vocab=256, layers=[F.latent(heads=4, dim=32, vdim=32, kv_rank=64, q_rank=64, window=20, mlp=F.dense(192)),
+                                                   F.delta(heads=2, kv_heads=1, dim=32, vdim=32, mlp=F.dense(64)),
+                                                   F.attention(heads=2, kv_heads=1, dim=32, window=12, mlp=F.dense(100))])
+    w = F.make_weights(cfg, 9)
+    prompts = {"a": _prompt(cfg, 70, 2), "b": _prompt(cfg, 9, 3)}
+    sched = [[("a", 40), ("b", 2)], [("b", 7), ("a", 1)]] + [[("a", 1)]] * 5 + [[("a", 24)]]
+    out = []
+    for fuse in ("1", "0"):
+        monkeypatch.setenv("B200_STACK_FUSE_GATE_UP", fuse)
+        r = F.make_runner(cfg, w, "bfloat16")
+        assert r.fuse_gate_up == (fuse == "1")
+        out.append(U.replay(U.make_engine(r), sched, prompts))
+        r.close()
+    for n in prompts:
+        assert np.array_equal(out[0][n], out[1][n]), n
+    want = O.forward(F.public_cfg(cfg), w, prompts["a"])[0].numpy()
+    e = U.rel_rms(out[0]["a"], want)
+    assert np.median(e) < 0.03 and e.max() < 0.15
+
+
 def test_greedy_generation_through_the_engines_own_scheduler(model_a, tmp_path):
     """A checkpoint directory goes through the registry (which sizes the delta layers from the tensor shapes), the weight loader,
     LLMEngine.generate and the scheduler (which hands out blocks and state slots and overlaps steps); prompts of unequal length
