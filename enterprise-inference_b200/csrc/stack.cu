@@ -317,6 +317,13 @@ static int stack_enqueue_step_postnorm(b200_ctx* c, const StepArgs& a, cudaStrea
   static const int plan_env = getenv("B200_STACK_ATTN_RUNS") ? atoi(getenv("B200_STACK_ATTN_RUNS")) : 1;
   if (!plan_env) attn_plan = 0;
   bool runs_built = false;   // the step's run list is in the attention workspace
+  // The run list is built by a launch of its own, once per step, before the first kernel that reads it: whether a layer's
+  // attention takes a kernel that walks runs depends on the layer's shape, so no attention call can be trusted to leave it.
+  auto step_runs = [&](bool& built) -> int {
+    if (built) return B200_OK;
+    built = true;
+    return paged_attn_runs_plan(a.row_to_seq, a.ctx_lens, T, M->attn_ws, s);
+  };
   float* x = M->x;
   // what the linears read: the stream itself in 32-bit mode, its rounded copy otherwise
   void* hin = f32 ? static_cast<void*>(x) : M->hn;
@@ -336,19 +343,17 @@ static int stack_enqueue_step_postnorm(b200_ctx* c, const StepArgs& a, cudaStrea
                                     L.heads, L.kv_heads, L.dim, L.vdim, m.block_size, m.norm_eps, s));
       const float* sink = (L.mixer_flags & B200_MIXF_SINK_ONE) ? M->zero_sink : nullptr;
       if (!f32 && paged_attn_mma_supported(L.heads, L.kv_heads, L.dim, L.vdim)) {
-        if (attn_plan != 2 && !runs_built) STEP(paged_attn_runs_plan(a.row_to_seq, a.ctx_lens, T, M->attn_ws, s));
-        runs_built = true;
-        if (attn_plan == 1) attn_plan = 2;
+        STEP(step_runs(runs_built));
         const int seen = L.window > 0 ? std::min(a.max_ctx, L.window + 64) : a.max_ctx;
         STEP(paged_attn_mma(M->q, (const __nv_bfloat16*)W.kc, (const __nv_bfloat16*)W.vc, a.block_table, a.bt_stride, a.row_to_seq, a.ctx_lens,
                             (__nv_bfloat16*)M->attn, static_cast<const int32_t*>(M->attn_ws) + 8, static_cast<const int32_t*>(M->attn_ws), T,
                             L.heads, L.kv_heads, L.dim, L.vdim, m.block_size, L.scale, sink, s,
                             latent_attn_splits(T, L.heads, L.vdim, seen, M->lat_ws_bytes), M->lat_ws, L.window));
       } else {
+      if (attn_plan) STEP(step_runs(runs_built));
       STEP(paged_attn_anydim(f32, M->q, W.kc, W.vc, a.block_table, a.bt_stride, a.row_to_seq, a.ctx_lens, a.positions, nullptr, max_pos,
-                             M->attn, T, L.heads, L.kv_heads, L.dim, L.vdim, m.block_size, L.scale, runs_built && attn_plan == 1 ? 2 : attn_plan,
-                             M->attn_ws, s, 0, 0, sink, L.window));
-      if (attn_plan == 1) attn_plan = 2, runs_built = true;
+                             M->attn, T, L.heads, L.kv_heads, L.dim, L.vdim, m.block_size, L.scale, attn_plan ? 2 : 0, M->attn_ws, s, 0, 0, sink,
+                             L.window));
       }
     } else if (is_latent(L)) {
       const int kr = L.kv_rank, hd = L.heads * L.dim;
@@ -358,18 +363,15 @@ static int stack_enqueue_step_postnorm(b200_ctx* c, const StepArgs& a, cudaStrea
       // q' = W_uk^T q: the scores are taken against the cached latent rows
       STEP(head_linear(f32, true, M->qh, hd, L.dim, W.uk_t, M->q, (int64_t)L.heads * kr, kr, nullptr, 0, 0, T, L.heads, kr, L.dim, s));
       if (!f32 && latent_attn_mma_supported(L.heads, kr, kr)) {
-        if (attn_plan != 2 && !runs_built) STEP(paged_attn_runs_plan(a.row_to_seq, a.ctx_lens, T, M->attn_ws, s));
-        runs_built = true;
-        if (attn_plan == 1) attn_plan = 2;
+        STEP(step_runs(runs_built));
         const int seen = L.window > 0 ? std::min(a.max_ctx, L.window + 64) : a.max_ctx;
         STEP(latent_attn_mma(M->q, (const __nv_bfloat16*)cache, a.block_table, a.bt_stride, a.row_to_seq, a.ctx_lens, (__nv_bfloat16*)M->lat,
                              static_cast<const int32_t*>(M->attn_ws) + 8, static_cast<const int32_t*>(M->attn_ws), T, L.heads, kr, kr,
                              m.block_size, L.scale, nullptr, s, latent_attn_splits(T, L.heads, kr, seen, M->lat_ws_bytes), M->lat_ws, L.window));
       } else {
+        if (attn_plan) STEP(step_runs(runs_built));
         STEP(paged_attn_anydim(f32, M->q, cache, cache, a.block_table, a.bt_stride, a.row_to_seq, a.ctx_lens, a.positions, nullptr, 1ll << 40,
-                               M->lat, T, L.heads, 1, kr, kr, m.block_size, L.scale, runs_built && attn_plan == 1 ? 2 : attn_plan, M->attn_ws, s,
-                               kr, kr, nullptr, L.window));
-        if (attn_plan == 1) attn_plan = 2, runs_built = true;
+                               M->lat, T, L.heads, 1, kr, kr, m.block_size, L.scale, attn_plan ? 2 : 0, M->attn_ws, s, kr, kr, nullptr, L.window));
       }
       const bool gate = (L.mixer_flags & B200_MIXF_HEAD_GATE) != 0;
       const char* gptr = static_cast<const char*>(M->qkv) + (int64_t)(L.q_rank + (L.kv_share > 0 ? 0 : kr)) * es;
@@ -429,6 +431,13 @@ static int stack_enqueue_step_parallel(b200_ctx* c, const StepArgs& a, cudaStrea
   static const int plan_env = getenv("B200_STACK_ATTN_RUNS") ? atoi(getenv("B200_STACK_ATTN_RUNS")) : 1;
   if (!plan_env) attn_plan = 0;
   bool runs_built = false;   // the step's run list is in the attention workspace
+  // The run list is built by a launch of its own, once per step, before the first kernel that reads it: whether a layer's
+  // attention takes a kernel that walks runs depends on the layer's shape, so no attention call can be trusted to leave it.
+  auto step_runs = [&](bool& built) -> int {
+    if (built) return B200_OK;
+    built = true;
+    return paged_attn_runs_plan(a.row_to_seq, a.ctx_lens, T, M->attn_ws, s);
+  };
   const int64_t rstride = (int64_t)m.max_tokens * Wd;
   float* u = M->x;
   int32_t* st_prev = reinterpret_cast<int32_t*>(M->state);
@@ -461,18 +470,15 @@ static int stack_enqueue_step_parallel(b200_ctx* c, const StepArgs& a, cudaStrea
                        L.dim, s));
       const float* sink = (L.mixer_flags & B200_MIXF_SINK) ? W.sink : nullptr;
       if (!f32 && latent_attn_mma_supported(L.heads, krow, L.kv_rank)) {
-        if (attn_plan != 2 && !runs_built) STEP(paged_attn_runs_plan(a.row_to_seq, a.ctx_lens, T, M->attn_ws, s));
-        runs_built = true;
-        if (attn_plan == 1) attn_plan = 2;
+        STEP(step_runs(runs_built));
         STEP(latent_attn_mma(M->q, (const __nv_bfloat16*)W.kc, a.block_table, a.bt_stride, a.row_to_seq, a.ctx_lens,
                              (__nv_bfloat16*)M->lat, static_cast<const int32_t*>(M->attn_ws) + 8, static_cast<const int32_t*>(M->attn_ws), T,
                              L.heads, krow, L.kv_rank, m.block_size, L.scale, sink, s,
                              latent_attn_splits(T, L.heads, L.kv_rank, a.max_ctx, M->lat_ws_bytes), M->lat_ws));
       } else {
+        if (attn_plan) STEP(step_runs(runs_built));
         STEP(paged_attn_anydim(f32, M->q, W.kc, W.kc, a.block_table, a.bt_stride, a.row_to_seq, a.ctx_lens, a.positions, nullptr, max_pos,
-                               M->lat, T, L.heads, 1, krow, L.kv_rank, m.block_size, L.scale, runs_built && attn_plan == 1 ? 2 : attn_plan,
-                               M->attn_ws, s, krow, krow, sink));
-        if (attn_plan == 1) attn_plan = 2, runs_built = true;
+                               M->lat, T, L.heads, 1, krow, L.kv_rank, m.block_size, L.scale, attn_plan ? 2 : 0, M->attn_ws, s, krow, krow, sink));
       }
       const bool gate = (L.mixer_flags & B200_MIXF_GATE) != 0;
       const char* gptr = static_cast<const char*>(M->qkv) + (int64_t)(L.heads * qh + krow) * es;
@@ -584,9 +590,12 @@ int stack_enqueue_step(b200_ctx* c, const StepArgs& a, cudaStream_t s) {
     } else {
       STEP(qk_norm_rotate_cache(f32, M->qkv, W.q_norm, W.k_norm, a.positions, a.slots, rot, L.rot_dims, vrot, M->q, W.kc, W.vc, T,
                                 L.heads, L.kv_heads, L.dim, L.vdim, m.block_size, m.norm_eps, max_pos, s));
+      if (attn_plan == 1) {   // the run list, by a launch of its own (a layer's shape decides whether its kernel walks runs)
+        STEP(paged_attn_runs_plan(a.row_to_seq, a.ctx_lens, T, M->attn_ws, s));
+        attn_plan = 2;
+      }
       STEP(paged_attn_anydim(f32, M->q, W.kc, W.vc, a.block_table, a.bt_stride, a.row_to_seq, a.ctx_lens, a.positions, vrot, max_pos,
                              M->attn, T, L.heads, L.kv_heads, L.dim, L.vdim, m.block_size, L.scale, attn_plan, M->attn_ws, s));
-      if (attn_plan == 1) attn_plan = 2;
     }
     STEP(stack_linear(c, M->attn, L.heads * L.vdim, W.o, M->y, Wd, T, Wd, L.heads * L.vdim, s));
     if (L.mlp == B200_MLP_MOE) {

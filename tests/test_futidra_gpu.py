@@ -374,6 +374,8 @@ ALONE = {
     "attention with every dimension turning, unscaled, window longer than the prompt": [F.attention(window=500, rot_dims=24, scaling=None)],
     "latent attention alone": [F.latent()],
     "latent attention reading the first layer's latents": [F.latent(window=4), F.latent(kv_from=0, heads=2, dim=8, vdim=16, q_rank=8, window=13)],
+    "a latent layer of more heads than the shared-tile kernel takes, then attention that walks the step's run list":
+        [F.latent(heads=12, dim=8, vdim=8, kv_rank=16, q_rank=16, window=20), F.attention()],
     "delta rule alone": [F.delta()],
     "delta rule, one tap, one q/k head for all heads": [F.delta(heads=3, kv_heads=1, conv=1, mlp=F.dense(24))],
 }
