@@ -24,10 +24,6 @@ def rms_norm(x, w, eps):
     return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * w
 
 
-def gelu_tanh(z):
-    return 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
-
-
 def rotary_frequencies(rot: dict) -> torch.Tensor:
     """f_i = base^(-2i/n) for the n/2 pairs, then the three-band wavelength rule when `scaling` is given."""
     n = int(rot["dims"])
@@ -227,46 +223,3 @@ def generate(cfg: dict, w, prompt: List[int], n: int) -> List[int]:
         out.append(int(torch.argmax(lg[-1])))
         toks.append(out[-1])
     return out
-
-
-def random_weights(cfg: dict, seed: int = 0, std: float = 0.08) -> Dict[str, torch.Tensor]:
-    """bf16-representable random weights with the checkpoint's tensor names."""
-    g = torch.Generator().manual_seed(seed)
-    W, V = int(cfg["width"]), int(cfg["vocab"])
-
-    def rnd(*shape, sd=std, mean=0.0):
-        return (torch.randn(*shape, generator=g) * sd + mean).to(torch.bfloat16)
-
-    w = {"embed": rnd(V, W, sd=1.0), "final.norm": rnd(W, sd=0.1, mean=1.0), "final.norm.b": rnd(W, sd=0.1)}
-    for i, L in enumerate(cfg["layers"]):
-        m, p = L["mixer"], f"l{i}."
-        w[p + "norm1"], w[p + "norm1.b"] = rnd(W, sd=0.1, mean=1.0), rnd(W, sd=0.1)
-        if L.get("mlp"):
-            ff = int(L["mlp"]["ff"])
-            w[p + "norm2"], w[p + "norm2.b"] = rnd(W, sd=0.1, mean=1.0), rnd(W, sd=0.1)
-            w[p + "mlp.gate"], w[p + "mlp.up"], w[p + "mlp.down"] = rnd(ff, W), rnd(ff, W), rnd(W, ff)
-        H, d, e = int(m["heads"]), int(m["dim"]), int(m["vdim"])
-        if L["type"] == "attention":
-            G = int(m["kv_heads"])
-            w[p + "mix.q"], w[p + "mix.k"] = rnd(H * d, W), rnd(G * d, W)
-            w[p + "mix.q.norm"], w[p + "mix.k.norm"] = rnd(d, sd=0.2, mean=1.0), rnd(d, sd=0.2, mean=1.0)
-            w[p + "mix.o"] = rnd(W, H * e)
-        elif L["type"] == "latent_attention":
-            r, qr = int(m["kv_rank"]), int(m["q_rank"])
-            w[p + "mix.dq"], w[p + "mix.dq.norm"], w[p + "mix.uq"] = rnd(qr, W), rnd(qr, sd=0.2, mean=1.0), rnd(H * d, qr, sd=0.2)
-            if m.get("kv_from") is None:
-                w[p + "mix.dkv"], w[p + "mix.dkv.norm"] = rnd(r, W), rnd(r, sd=0.2, mean=1.0)
-            w[p + "mix.uk"], w[p + "mix.uv"] = rnd(H * d, r, sd=0.2), rnd(H * e, r, sd=0.2)
-            w[p + "mix.g"], w[p + "mix.o"] = rnd(H, W), rnd(W, H * e)
-        else:
-            G, taps = int(m["kv_heads"]), int(m["conv"])
-            lr = max(4, W // 8)
-            w[p + "mix.q"], w[p + "mix.k"], w[p + "mix.v"] = rnd(G * d, W), rnd(G * d, W), rnd(H * e, W)
-            for n_, ch in (("q", G * d), ("k", G * d), ("v", H * e)):
-                w[p + f"mix.{n_}.conv"] = rnd(ch, taps, sd=0.5)
-            w[p + "mix.b"], w[p + "mix.A_log"] = rnd(H, W), rnd(H, sd=0.5)
-            w[p + "mix.norm"] = rnd(e, sd=0.2, mean=1.0)
-            w[p + "mix.a1"], w[p + "mix.a2"], w[p + "mix.dt_bias"] = rnd(lr, W), rnd(H * d, lr, sd=0.3), rnd(H * d, sd=0.5)
-            w[p + "mix.g1"], w[p + "mix.g2"] = rnd(lr, W), rnd(H * e, lr, sd=0.3)
-            w[p + "mix.o"] = rnd(W, H * e)
-    return w

@@ -152,3 +152,11 @@ def test_oracle_shared_latents_and_portions_of_the_recurrence():
     for lo, n in ((0, 1), (1, 2), (3, 1), (4, 9), (13, 17)):
         parts.append(O.channel_delta_mixer(h[lo:lo + n], p, m, 1e-5, state=st))
     assert torch.allclose(torch.cat(parts), whole, atol=1e-10)
+
+
+def test_oracle_convolution_taps_and_start():
+    x = torch.arange(1.0, 9.0, dtype=torch.float64).reshape(4, 2)
+    w = torch.tensor([[0.5, -1.0, 2.0], [0.0, 0.0, 1.0]], dtype=torch.float64)        # last column: the current token
+    y = O.causal_conv_silu(x, w)
+    pre = torch.tensor([[2.0 * 1, 2.0], [2.0 * 3 - 1.0 * 1, 4.0], [2.0 * 5 - 3.0 + 0.5 * 1, 6.0], [2.0 * 7 - 5.0 + 0.5 * 3, 8.0]], dtype=torch.float64)
+    assert torch.allclose(y, pre * torch.sigmoid(pre))
