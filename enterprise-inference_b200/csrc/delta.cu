@@ -16,7 +16,8 @@
 //    owns 4 columns, a lane the key channels lane, lane + 32, ...; the state lives in registers during the walk and is
 //    stored [head][vdim][dim] so that a warp's loads are contiguous.  The step's rows are staged 16 at a time in shared memory,
 //    the next stage travelling into registers while this one is walked.  The only reductions on the chain from one row to the
-//    next are the four S^T k sums of a warp (interleaved shuffles); the read-out sums overlap the next row.
+//    next are the four S^T k sums of a warp (interleaved shuffles); the read-out leaves per-lane partial sums in shared
+//    memory that are added for the whole stage after its walk.
 //    A sequence whose first row of the step is at position 0 starts from zeros, whatever the slot held.
 #include "common.cuh"
 
@@ -195,6 +196,7 @@ delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
   float* sg = sk + kDsStage * dim;
   float* sv = sg + kDsStage * dim;         // [kDsStage][32]
   float* sb = sv + kDsStage * kDsBlockCols;   // [kDsStage]
+  float* mypart = sb + kDsStage + warp * (kDsStage * kDsCols * 33);   // [kDsStage][kDsCols][32 lanes + 1]
   constexpr int EQ = 2 * DPL, EV = kDsStage * kDsBlockCols / kDsThreads;   // elements per thread of a [16][dim] / [16][32] tile
   float rq[EQ], rk[EQ], rg[EQ], rv[EV], rb = 0.f;
   auto prefetch = [&](int b0) {
@@ -233,6 +235,8 @@ delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
     if (threadIdx.x < kDsStage) sb[threadIdx.x] = rb;
     __syncthreads();
     if (b0 + kDsStage < n_rows) prefetch(b0 + kDsStage);
+    // the walk: state update and per-lane partial read-out sums only; the one reduction on the chain from a row to the next is
+    // S^T k.  The read-out sums over lanes follow for the whole stage.
     for (int r = 0; r < nb; ++r) {
       float q[DPL], k[DPL], dot[kDsCols], acc[kDsCols], v[kDsCols];
 #pragma unroll
@@ -267,17 +271,18 @@ delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
           Sr[c][i] = fmaf(k[i], u, Sr[c][i]);
           acc[c] = fmaf(Sr[c][i], q[i], acc[c]);
         }
+        mypart[(r * kDsCols + c) * 33 + lane] = acc[c];
       }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1)
-#pragma unroll
-        for (int c = 0; c < kDsCols; ++c) acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], o);
-      float mine = 0.f;
-#pragma unroll
-      for (int c = 0; c < kDsCols; ++c)
-        if (lane == c) mine = acc[c];
-      if (lane < kDsCols && j0 + lane < vd) out[(int64_t)(start + b0 + r) * hv + h * vd + j0 + lane] = mine;
     }
+    __syncwarp();
+    for (int x = lane; x < nb * kDsCols; x += 32) {   // lane x adds the 32 partials of sum x in lane order
+      float sum = 0.f;
+#pragma unroll 8
+      for (int l = 0; l < 32; ++l) sum += mypart[x * 33 + l];
+      const int r = x / kDsCols, c = x % kDsCols;
+      if (j0 + c < vd) out[(int64_t)(start + b0 + r) * hv + h * vd + j0 + c] = sum;
+    }
+    __syncwarp();
   }
 #pragma unroll
   for (int i = 0; i < DPL; ++i) {
@@ -362,11 +367,11 @@ int delta_scan(const float* qn, const float* kn, const float* vn, const float* b
   B200_REQUIRE(positions && seq_start && seq_slots && state, B200_ERR_INVALID, "delta_scan: null argument");
   const dim3 grid(S, heads, (vd + kDsBlockCols - 1) / kDsBlockCols), block(kDsThreads);
   const int dpl = (dim + 31) / 32;
-  const size_t smem = (size_t)kDsStage * (3 * dim + kDsBlockCols + 1) * 4;   // <= 51 KiB
+  const size_t smem = (size_t)kDsStage * (3 * dim + kDsBlockCols + 1 + kDsWarps * kDsCols * 33) * 4;   // <= 117 KiB
 #define SCAN(D)                                                                                                                       \
   do {                                                                                                                                \
     static bool done[64] = {};                                                                                                        \
-    if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(delta_scan_kernel<D>, 64 * 1024, done));                                      \
+    if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(delta_scan_kernel<D>, 128 * 1024, done));                                      \
     B200_CUDA(launch(delta_scan_kernel<D>, grid, block, smem, s, qn, kn, vn, beta, decay, positions, seq_start, seq_slots, state,     \
                      slot_stride, out, heads, kv_heads, dim, vd));                                                                    \
   } while (0)
