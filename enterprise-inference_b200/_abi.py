@@ -29,7 +29,8 @@ class StackLayer(C.Structure):
                [("scale", C.c_float)] + [(n, C.c_int32) for n in ("mlp", "experts", "top", "groups", "keep", "ff")] + \
                [(n, C.c_int32) for n in ("kv_rank", "rot_dim", "mixer_flags")] + [("gate_cap", C.c_float)] + \
                [(n, C.c_int32) for n in ("act", "ungated", "sigmoid_scores", "weight_input", "shared_ff")] + \
-               [(n, C.c_int32) for n in ("window", "q_rank", "kv_share", "conv_taps", "decay_rank", "gate_rank")]
+               [(n, C.c_int32) for n in ("window", "q_rank", "kv_share", "conv_taps", "decay_rank", "gate_rank", "norm_groups")] + \
+               [("act_limit", C.c_float), ("route_chosen", C.c_int32)]
 
 
 class StackCfg(C.Structure):
@@ -37,23 +38,29 @@ class StackCfg(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("width", "vocab", "n_layers")] + [("embed_scale", C.c_float), ("norm_eps", C.c_float)] + \
                [(n, C.c_int32) for n in ("f32", "block_size", "max_tokens", "max_blocks_per_seq", "max_logit_rows")] + \
                [(n, C.c_int32) for n in ("form", "canon_taps", "depth_avg", "bigram_buckets", "bigram_mul_prev", "bigram_mul_cur")] + \
-               [("logit_softcap", C.c_float), ("n_state_slots", C.c_int32), ("residual_alpha", C.c_float)]
+               [("logit_softcap", C.c_float), ("n_state_slots", C.c_int32), ("residual_alpha", C.c_float), ("streams", C.c_int32),
+                ("residual_mult", C.c_float)]
 
 
-MIXER_ATTENTION, MIXER_LATENT, MIXER_MLSTM, MIXER_DELTA = 1, 2, 3, 4
+MIXER_ATTENTION, MIXER_LATENT, MIXER_MLSTM, MIXER_DELTA, MIXER_SSD = 1, 2, 3, 4, 5
 MLP_NONE, MLP_MOE, MLP_DENSE = 0, 1, 2
-ACT_SILU, ACT_GELU_TANH, ACT_RELU2, ACT_RELU = 0, 1, 2, 3
-ACTS = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH, "relu2": ACT_RELU2, "relu": ACT_RELU}
-FORM_SANDWICH, FORM_PARALLEL, FORM_POSTNORM = 0, 1, 2
+ACT_SILU, ACT_GELU_TANH, ACT_RELU2, ACT_RELU, ACT_SWIGLU_CLAMP, ACT_POLYNORM = 0, 1, 2, 3, 4, 5
+ACTS = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH, "relu2": ACT_RELU2, "relu": ACT_RELU, "swiglu_clamp": ACT_SWIGLU_CLAMP,
+        "polynorm": ACT_POLYNORM}
+FORM_SANDWICH, FORM_PARALLEL, FORM_POSTNORM, FORM_HYPER = 0, 1, 2, 3
 MIXF_SINK, MIXF_GATE, MIXF_HEAD_NORM, MIXF_VALUE_IS_KEY, MIXF_SINK_ONE, MIXF_HEAD_GATE = 1, 2, 4, 8, 16, 32
+MIXF_ROT_HALF, MIXF_NO_QK_NORM, MIXF_HEAD_DECAY = 64, 128, 256
+MAX_STREAMS = 8
 (SW_EMBED, SW_FINAL_NORM, SW_HEAD, SW_NORM_MIX_PRE, SW_NORM_MIX_POST, SW_NORM_MLP_PRE, SW_NORM_MLP_POST, SW_QKV, SW_Q_NORM,
  SW_K_NORM, SW_O, SW_ROUTER, SW_ROUTER_BIAS, SW_EXPERT_GATE_UP, SW_EXPERT_DOWN, SW_BIGRAM, SW_CANON, SW_DEPTH_AVG, SW_UK_T, SW_UV,
  SW_SINK, SW_GATES, SW_GATES_BIAS, SW_HEAD_NORM, SW_MLP_GATE_UP, SW_MLP_DOWN, SW_SHARED_UP, SW_SHARED_DOWN, SW_NORM_MIX_POST_BIAS,
  SW_NORM_MLP_POST_BIAS, SW_FINAL_NORM_BIAS, SW_Q_LATENT_NORM, SW_UQ, SW_CONV, SW_DECAY_UP, SW_DECAY_BIAS, SW_DECAY_LOG,
- SW_GATE_UP, SW_MLP_GATE_UP_INTERLEAVED) = range(39)
+ SW_GATE_UP, SW_MLP_GATE_UP_INTERLEAVED, SW_NORM_MIX_PRE_BIAS, SW_NORM_MLP_PRE_BIAS, SW_SCALE_MIX, SW_SCALE_MLP, SW_HC_MIX, SW_HC_MLP,
+ SW_CANON_MLP, SW_CONV_BIAS, SW_SKIP, SW_MLP_ACT) = range(49)
 SW_F32 = {SW_FINAL_NORM, SW_NORM_MIX_PRE, SW_NORM_MIX_POST, SW_NORM_MLP_PRE, SW_NORM_MLP_POST, SW_Q_NORM, SW_K_NORM, SW_ROUTER_BIAS,
           SW_CANON, SW_DEPTH_AVG, SW_SINK, SW_GATES_BIAS, SW_HEAD_NORM, SW_NORM_MIX_POST_BIAS, SW_NORM_MLP_POST_BIAS,
-          SW_FINAL_NORM_BIAS, SW_Q_LATENT_NORM, SW_CONV, SW_DECAY_BIAS, SW_DECAY_LOG}
+          SW_FINAL_NORM_BIAS, SW_Q_LATENT_NORM, SW_CONV, SW_DECAY_BIAS, SW_DECAY_LOG, SW_NORM_MIX_PRE_BIAS, SW_NORM_MLP_PRE_BIAS,
+          SW_SCALE_MIX, SW_SCALE_MLP, SW_HC_MIX, SW_HC_MLP, SW_CANON_MLP, SW_CONV_BIAS, SW_SKIP, SW_MLP_ACT}
 
 W_EMBED, W_LN1, W_QKV, W_QKV_BIAS, W_O, W_LN2, W_GATE_UP, W_DOWN, W_FINAL_NORM, W_LM_HEAD, W_GATE_UP_INTERLEAVED = range(11)
 
@@ -169,6 +176,21 @@ SIGNATURES = {
     "b200_delta_tails": (C.c_int, [_i32, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _vp]),
     "b200_delta_scan": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _i32, _i32, _i32, _i32, _i32, _vp]),
     "b200_moe_experts_form": (C.c_int, [_i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _i32, _i32, _i32, _vp]),
+    "b200_hyper_step": (C.c_int, [_i32, _vp, _i64, _i32, _i32, _vp, _vp, _i32, _vp, _vp, _f32, _vp, _vp, _vp, _f32, _vp, _vp, _vp, _vp, _i32,
+                                  _i32, _vp]),
+    "b200_qkv_rotate_cache": (C.c_int, [_i32, _vp, _i64, _vp, _vp, _vp, _i32, _i32, _i64, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp]),
+    "b200_polynorm": (C.c_int, [_i32, _vp, _vp, _vp, _i32, _i32, _f32, _vp]),
+    "b200_ff_act_limit": (C.c_int, [_i32, _vp, _vp, _i32, _i32, _i32, _i32, _f32, _vp]),
+    "b200_moe_route_chosen": (C.c_int, [_i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),
+    "b200_moe_experts_limit": (C.c_int, [_i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _i32, _i32, _f32, _vp]),
+    "b200_delta_prep_head": (C.c_int, [_i32, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32,
+                                       _i32, _i32, _i32, _vp]),
+    "b200_linear_scan": (C.c_int, [_i32, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _i64, _vp, _i32, _i32, _i32, _i32, _i32,
+                                   _vp]),
+    "b200_head_norm_gate_act": (C.c_int, [_i32, _vp, _vp, _vp, _i64, _vp, _i32, _i32, _i32, _f32, _i32, _vp]),
+    "b200_ssd_prep": (C.c_int, [_i32, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32,
+                                _i32, _i32, _i32, _vp]),
+    "b200_ssd_gate_norm": (C.c_int, [_i32, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _i32, _i32, _i32, _i32, _f32, _vp]),
 }
 
 _lib = None

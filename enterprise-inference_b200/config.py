@@ -201,6 +201,9 @@ class AttentionSpec:
     head_norm: bool = False                # q/k RMS norm per head with one weight of `dim` entries (else over the whole projection)
     value_is_key: bool = False             # no value projection: a value is the key projection before norm and rotation
     sink_one: bool = False                 # one more unit in the softmax denominator
+    qk_norm: bool = True                   # False: plain q/k/v projections, no norm of q and k at all
+    rot_half: bool = False                 # rotated dimension i pairs with i + rot.dims / 2 (else 2i with 2i + 1)
+    sink: bool = False                     # a learned per-head term exp(sink) in the softmax denominator
 
 
 @dataclass
@@ -214,7 +217,7 @@ class MoESpec:
 
 @dataclass
 class StackLayerSpec:
-    mixer: object                     # AttentionSpec | LatentAttentionSpec | ChannelDeltaSpec
+    mixer: object                     # AttentionSpec | LatentAttentionSpec | ChannelDeltaSpec | HeadDeltaSpec | StateSpaceSpec
     mlp: Optional[object] = None      # MoESpec | FeedForwardSpec
 
 
@@ -342,6 +345,9 @@ class FeedForwardSpec:
     experts: int = 0
     top: int = 0
     shared_ff: int = 0
+    gated: Optional[bool] = None           # None: the design's default shape (dense gated, experts ungated)
+    limit: float = 0.0                     # act "swiglu_clamp": min(gate, limit) * sigmoid(1.702 gate) * (clamp(up, +-limit) + 1)
+    router: str = ""                       # "chosen_softmax": bias inside the logits, weights = softmax over the chosen logits
 
 
 @dataclass
@@ -586,6 +592,142 @@ class FutidraConfig:
                              postln_alpha=float(c.get("postln_alpha", 1.0)), layers=layers)
 
 
+# ---- Rudolix ----------------------------------------------------------------------------------------------------------------
+@dataclass
+class HeadDeltaSpec:
+    """Delta-rule recurrence with ONE decay per head: q/k in `kv_heads` heads of `dim`, values in `heads` heads of `vdim`, a causal
+    convolution of `conv` taps and silu on q, k and v, beta and the decay from single projections, read-out times a weight shared by
+    the heads and silu of a gate projection."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    conv: int
+    kind: str = "head_delta"
+
+
+@dataclass
+class StateSpaceSpec:
+    """State-space recurrence (scalar decay per head): `heads` heads of `vdim` channels, `groups` shared B / C vectors of `state`
+    entries, a causal convolution of `conv` taps with bias over x | B | C, the gated output normalised in `norm_groups` parts."""
+    heads: int
+    vdim: int
+    state: int
+    groups: int
+    norm_groups: int
+    conv: int
+    kind: str = "ssd"
+
+
+@dataclass
+class RudolixConfig:
+    """Rudolix: decoder-only, pre-norm sublayers over `streams` copies of the residual (hyper-connections): a sublayer reads a
+    weighted sum of the streams through a layer norm with weight and bias and a causal per-channel input convolution, and its result,
+    scaled per channel and by `residual_mult`, is dealt back to every stream while the streams are mixed by a matrix.  Mixers:
+    grouped-query attention with half-layout partial rotation and a learned sink, the gated delta rule with one decay per head, the
+    Mamba-2 state-space recurrence.  Feed-forwards: ungated dense with a polynomial of unit-RMS powers, or routed experts (softmax over
+    the chosen logits, clamped gated experts).  The output projection is the embedding table."""
+    name: str = "rudolix"
+    width: int = 256
+    vocab: int = 1024
+    embed_scale: float = 1.0
+    norm_eps: float = 1e-6
+    canon_taps: int = 0
+    streams: int = 1
+    residual_mult: float = 1.0
+    layers: List[StackLayerSpec] = field(default_factory=list)
+    architecture: str = "Rudolix"
+
+    @property
+    def hidden(self) -> int:
+        return self.width
+
+    @property
+    def n_layers(self) -> int:
+        return len(self.layers)
+
+    @property
+    def needs_state(self) -> bool:
+        return self.canon_taps > 1 or any(isinstance(L.mixer, (HeadDeltaSpec, StateSpaceSpec)) for L in self.layers)
+
+    def to_dict(self):
+        return asdict(self)
+
+    def mixer_rows(self, a) -> int:
+        """Rows of the fused projection of a mixer's input."""
+        if isinstance(a, HeadDeltaSpec):
+            return 2 * a.kv_heads * a.dim + 2 * a.heads * a.vdim + 2 * a.heads
+        if isinstance(a, StateSpaceSpec):
+            return 2 * a.heads * a.vdim + 2 * a.groups * a.state + a.heads
+        return a.heads * a.dim + a.kv_heads * (a.dim + a.vdim)
+
+    def _layer_params(self, L, active_only: bool) -> int:
+        W, a = self.width, L.mixer
+        n = W * self.mixer_rows(a) + a.heads * a.vdim * W
+        f = L.mlp
+        if f is not None and f.kind == "dense":
+            n += 2 * f.ff * W
+        elif f is not None:
+            n += f.experts * W + (f.top if active_only else f.experts) * 3 * f.ff * W
+        return n
+
+    def decode_params(self) -> int:
+        """Weights one decode row touches (chosen experts only)."""
+        return self.vocab * self.width + sum(self._layer_params(L, True) for L in self.layers)
+
+    def weight_bytes(self) -> int:
+        return 2 * (self.vocab * self.width + sum(self._layer_params(L, False) for L in self.layers))
+
+    def kv_bytes_per_token(self, f32: bool = False) -> int:
+        return sum(L.mixer.kv_heads * (L.mixer.dim + L.mixer.vdim) for L in self.layers if isinstance(L.mixer, AttentionSpec)) * (4 if f32 else 2)
+
+    @staticmethod
+    def from_dict(c: dict, name: str = "rudolix") -> "RudolixConfig":
+        layers = []
+        for i, l in enumerate(c["layers"]):
+            kind, m = l.get("type"), l["mixer"]
+            if kind == "attention":
+                rot = None
+                r = m.get("rot")
+                if r and int(r.get("dims", 0)) > 0:
+                    rot = RotarySpec(base=float(r["base"]), dims=int(r["dims"]))
+                    if rot.dims % 2 or rot.dims > int(m["dim"]):
+                        raise ValueError(f"layer {i}: {rot.dims} rotated dimensions in heads of {m['dim']}")
+                mixer = AttentionSpec(heads=int(m["heads"]), kv_heads=int(m.get("kv_heads", m["heads"])), dim=int(m["dim"]),
+                                      vdim=int(m.get("vdim", m["dim"])), scale=float(m["scale"]), rot=rot, qk_norm=False, rot_half=True, sink=True)
+            elif kind == "delta":
+                mixer = HeadDeltaSpec(heads=int(m["heads"]), kv_heads=int(m.get("kv_heads", m["heads"])), dim=int(m["dim"]), vdim=int(m["vdim"]),
+                                      conv=int(m.get("conv", 1)))
+            elif kind == "mamba2":
+                mixer = StateSpaceSpec(heads=int(m["heads"]), vdim=int(m["vdim"]), state=int(m["state"]), groups=int(m.get("groups", 1)),
+                                       norm_groups=int(m.get("norm_groups", 1)), conv=int(m.get("conv", 1)))
+                if mixer.heads % mixer.groups or (mixer.heads * mixer.vdim) % mixer.norm_groups:
+                    raise ValueError(f"layer {i}: {mixer.heads} heads of {mixer.vdim} over {mixer.groups} groups and {mixer.norm_groups} norm parts")
+            else:
+                raise ValueError(f"layer {i}: unsupported mixer type {kind!r} (this design has attention, delta, mamba2)")
+            if not isinstance(mixer, StateSpaceSpec) and mixer.heads % mixer.kv_heads:
+                raise ValueError(f"layer {i}: {mixer.heads} heads over {mixer.kv_heads} key heads")
+            mlp = None
+            f = l.get("mlp")
+            if f:
+                if f.get("kind") == "dense":
+                    mlp = FeedForwardSpec(kind="dense", ff=int(f["ff"]), act="polynorm", gated=False)
+                elif f.get("kind") == "moe":
+                    mlp = FeedForwardSpec(kind="moe", ff=int(f["expert"]["ff"]), act="swiglu_clamp", experts=int(f["router"]["experts"]),
+                                          top=int(f["router"]["top"]), gated=True, limit=float(f["expert"]["limit"]), router="chosen_softmax")
+                    if not 0 < mlp.top <= mlp.experts:
+                        raise ValueError(f"layer {i}: top {mlp.top} of {mlp.experts} experts")
+                else:
+                    raise ValueError(f"layer {i}: unsupported feed-forward kind {f.get('kind')!r}")
+            layers.append(StackLayerSpec(mixer=mixer, mlp=mlp))
+        streams = int(c.get("streams", 1))
+        if not 1 <= streams <= 8:
+            raise ValueError(f"{streams} residual streams (1 to 8 are served)")
+        return RudolixConfig(name=name, width=int(c["width"]), vocab=int(c["vocab"]), embed_scale=float((c.get("embedding") or {}).get("scale", 1.0)),
+                             norm_eps=float((c.get("norm") or {}).get("eps", 1e-6)), canon_taps=int((c.get("canon") or {}).get("taps", 0)),
+                             streams=streams, residual_mult=float(c.get("residual_mult", 1.0)), layers=layers)
+
+
 def checkpoint_shapes(path: str) -> Dict[str, list]:
     """Tensor name -> shape of every *.safetensors file under `path`, from the files' headers alone (8-byte little-endian
     length, then that many bytes of JSON)."""
@@ -603,7 +745,8 @@ def checkpoint_shapes(path: str) -> Dict[str, list]:
 
 
 # config.json "architecture" -> reader.  HF-style configs (model_type) go through from_hf_config.
-ARCHITECTURES = {"Bopilorn": BopilornConfig.from_dict, "Dupolorn": DupolornConfig.from_dict, "Futidra": FutidraConfig.from_dict}
+ARCHITECTURES = {"Bopilorn": BopilornConfig.from_dict, "Dupolorn": DupolornConfig.from_dict, "Futidra": FutidraConfig.from_dict,
+                 "Rudolix": RudolixConfig.from_dict}
 NEEDS_SHAPES = {"Futidra"}   # readers that take the checkpoint's tensor shapes for sizes config.json does not name
 
 

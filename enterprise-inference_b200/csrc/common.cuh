@@ -89,6 +89,16 @@ __device__ __forceinline__ float act_apply(float z, int kind) {
   }
   return z / (1.0f + expf(-z));
 }
+// gate and up value of a gated feed-forward -> the activated product.  B200_ACT_SWIGLU_CLAMP: g = min(g, limit),
+// u = clamp(u, -limit, limit), g * sigmoid(1.702 g) * (u + 1)
+__device__ __forceinline__ float gate_combine(float g, float u, int kind, float limit) {
+  if (kind == B200_ACT_SWIGLU_CLAMP) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+  }
+  return act_apply(g, kind) * u;
+}
 
 // ---- Programmatic dependent launch -------------------------------------------------------
 // Every kernel of the step waits for its predecessor's memory here and lets its successor
@@ -320,16 +330,18 @@ int latent_attn_splits(int T, int heads, int rank, int max_ctx, int64_t ws_bytes
 int64_t moe_workspace_bytes(int T, int top, int experts, int width, int ff);
 bool moe_tc_supported(int width, int ff);
 // logits_ws ([T][experts] fp32) given and bf16 rows: the logits come from the tcgen05 linear (lin_ws: its split-K workspace)
-// sigmoid_scores: every expert's score is the sigmoid of its logit (no softmax over the experts)
+// score_mode 0: softmax over all experts, the bias joins the choice only; 1: every expert's score is the sigmoid of its logit;
+// 2: the bias joins the logits, the largest logits are chosen, weights = softmax over the chosen logits
 int moe_route(bool f32, const void* x, const __nv_bfloat16* w_router, const float* bias, int T, int width, int experts, int top,
               int groups, int keep, int32_t* out_ids, float* out_w, cudaStream_t s, float* logits_ws = nullptr,
-              void* lin_ws = nullptr, int64_t lin_ws_bytes = 0, bool sigmoid_scores = false);
+              void* lin_ws = nullptr, int64_t lin_ws_bytes = 0, int score_mode = 0);
 // The shape of an expert: gated = down(act(gate x) * (up x)) over [expert][2 ff][width], else down(act(up x)) over
 // [expert][ff][width]; weight_input: the mixing weight scales the expert's input row instead of its output row.
 struct ExpertForm {
   bool gated = true;
   int act = B200_ACT_SILU;
   bool weight_input = false;
+  float limit = 0.f;   // B200_ACT_SWIGLU_CLAMP
 };
 int moe_experts(bool f32, const void* x, const __nv_bfloat16* w_gu, const __nv_bfloat16* w_down, const int32_t* ids,
                 const float* wts, int T, int width, int ff, int experts, int top, float* parts, void* ws, cudaStream_t s,
@@ -349,7 +361,7 @@ int canon_conv(bool f32, const float* h, const float* w, void* out, int T, int w
                const int32_t* row_to_seq, const int32_t* seq_start, const int32_t* seq_slots, float* tails, int64_t slot_stride,
                cudaStream_t s);
 int rms_rows(bool f32, const float* u, const int32_t* rows, const float* g, void* out, int R, int width, float eps, cudaStream_t s);
-int ff_act(bool f32, const void* in, void* out, int T, int ff, bool gated, int kind, cudaStream_t s);
+int ff_act(bool f32, const void* in, void* out, int T, int ff, bool gated, int kind, cudaStream_t s, float limit = 0.f);
 int logit_cap(const float* in, float* out_f32, __nv_bfloat16* out_bf16, int R, int vocab, int ld, float cap, cudaStream_t s);
 int latent_prep(bool f32, const void* qkv, int64_t ld, const float* norm_w, const int32_t* positions, const int32_t* slots,
                 const float* rot, int rot_dims, int64_t max_pos, float* qfull, void* cache, int T, int heads, int dim, int rot_dim,
@@ -364,7 +376,7 @@ int mlstm_scan(bool f32, const void* qkv, int64_t ld, int q_off, int k_off, int 
                const int32_t* seq_start, const int32_t* seq_slots, float* state, int64_t slot_stride, float* out, int S, int heads,
                int dim, int vd, cudaStream_t s, bool single_rows = false);   // single_rows: every sequence of the step has one row
 int head_norm_gate(bool f32, const float* o, const float* w, const void* gate, int64_t ldg, void* out, int T, int heads, int vd, float eps,
-                   cudaStream_t s);
+                   cudaStream_t s, bool gate_silu = false);   // gate_silu: times silu(gate) instead of sigmoid(gate)
 // post-norm layer form (postnorm.cu): layer norm with bias after the sum; attention whose values are its raw keys with per-head
 // q/k norms; the two norms of a latent mixer with a query latent
 int postnorm_stream(bool f32, const float* x_in, const void* y, float alpha, const float* w, const float* b, float* x_out, void* out_act,
@@ -381,7 +393,27 @@ int64_t delta_tail_floats(int heads, int kv_heads, int dim, int vd, int taps);
 int delta_prep(bool f32, const void* fused, int64_t ld, const void* a2, const float* conv_w, const float* dt_bias, const float* a_log,
                const int32_t* positions, const int32_t* row_to_seq, const int32_t* seq_start, const int32_t* seq_slots, const float* tails,
                int64_t slot_stride, float* qn, float* kn, float* vn, float* beta, float* decay, int T, int heads, int kv_heads, int dim,
-               int vdim, int taps, int decay_rank, int gate_rank, cudaStream_t s);
+               int vdim, int taps, int decay_rank, int gate_rank, cudaStream_t s, bool head_decay = false);
+// the scan with the decay of (row, head, channel) at decay[t * g_row + h * g_head + d * g_chan]; delta_rule false: u = beta v
+int linear_scan(bool delta_rule, const float* qn, const float* kn, const float* vn, const float* beta, const float* decay, int64_t g_row,
+                int g_head, int g_chan, const int32_t* positions, const int32_t* seq_start, const int32_t* seq_slots, float* state,
+                int64_t slot_stride, float* out, int S, int heads, int kv_heads, int dim, int vd, cudaStream_t s);
+// state-space mixer (ssd.cu)
+int64_t ssd_tail_floats(int heads, int groups, int state, int vdim, int taps);
+int ssd_prep(bool f32, const void* fused, int64_t ld, const float* conv_w, const float* conv_b, const float* dt_bias, const float* a_log,
+             const int32_t* positions, const int32_t* row_to_seq, const int32_t* seq_start, const int32_t* seq_slots, const float* tails,
+             int64_t slot_stride, float* xn, float* bn, float* cn, float* dt, float* decay, int T, int heads, int groups, int state, int vdim,
+             int taps, cudaStream_t s);
+int ssd_gate_norm(bool f32, const float* o, const float* xn, const float* skip, const void* z, int64_t ldz, const float* w, void* out, int T,
+                  int heads, int vdim, int norm_groups, float eps, cudaStream_t s);
+// multi-stream pre-norm layer form (hyper.cu)
+int hyper_step(bool f32, float* X, int64_t sstride, int n, bool init, const void* y, const float* parts, int n_parts, const float* scale,
+               const float* hc, float mult, const float* open_in, const float* nw, const float* nb, float eps, const int32_t* rows,
+               float* h_f32, void* h_act, float* sum_out, int R, int width, cudaStream_t s);
+int qkv_rotate_cache(bool f32, const void* qkv, int64_t ld, const int32_t* positions, const int32_t* slots, const float* rot, int rot_dims,
+                     bool half_layout, int64_t max_pos, float* qout, void* kc, void* vc, int T, int heads, int kv_heads, int dim, int vdim,
+                     int block_size, cudaStream_t s);
+int polynorm(bool f32, const void* z, const float* coef, void* out, int T, int ff, float eps, cudaStream_t s);
 int delta_tails(bool f32, const void* fused, int64_t ld, const int32_t* positions, const int32_t* seq_start, const int32_t* seq_slots,
                 float* tails, int64_t slot_stride, int S, int channels, int taps, cudaStream_t s);
 int delta_scan(const float* qn, const float* kn, const float* vn, const float* beta, const float* decay, const int32_t* positions,

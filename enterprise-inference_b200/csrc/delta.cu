@@ -19,6 +19,12 @@
 //    next are the four S^T k sums of a warp (interleaved shuffles); the read-out leaves per-lane partial sums in shared
 //    memory that are added for the whole stage after its walk.
 //    A sequence whose first row of the step is at position 0 starts from zeros, whatever the slot held.
+//
+// Two parameters widen the kernels to other recurrences of the same shape.  The decay of (row, head, key channel) is read at
+// decay[t * g_row + h * g_head + d * g_chan]: channel decays are (heads*dim, dim, 1), ONE decay per head is (heads, 1, 0), and
+// delta_prep then takes the decay's pre-activation straight from the fused row (one column per head, decay_dim 1) instead of a
+// second-step projection.  DELTA false drops the correction: u = beta v, which is the state-space recurrence
+// S = g S + dt B x^T, y = S^T C of ssd.cu with keys B, queries C, values x and beta = dt.
 #include "common.cuh"
 
 namespace b200 {
@@ -35,7 +41,7 @@ constexpr int kPrepThreads = 256;
 
 template <typename AT>
 __global__ void __launch_bounds__(kPrepThreads)
-delta_prep_kernel(const AT* __restrict__ fused, int64_t ld, const AT* __restrict__ a2, const float* __restrict__ conv_w,
+delta_prep_kernel(const AT* __restrict__ fused, int64_t ld, const AT* __restrict__ a2, int64_t a2_ld, int decay_dim, const float* __restrict__ conv_w,
                   const float* __restrict__ dt_bias, const float* __restrict__ a_log, const int32_t* __restrict__ positions,
                   const int32_t* __restrict__ row_to_seq, const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slots,
                   const float* __restrict__ tails, int64_t slot_stride, float* __restrict__ qn, float* __restrict__ kn,
@@ -47,11 +53,11 @@ delta_prep_kernel(const AT* __restrict__ fused, int64_t ld, const AT* __restrict
   const int64_t t = blockIdx.x;
   const int qk = kv_heads * dim, C = 2 * qk + heads * vdim;
   if (blockIdx.y == 1) {   // the second CTA of a row: beta and the decays (nothing of the convolution enters them)
-    const int hd = heads * dim;
+    const int hd = heads * decay_dim;   // decay_dim: dim (one decay per key channel) or 1 (one per head)
     for (int h = threadIdx.x; h < heads; h += kPrepThreads) beta[t * heads + h] = sigmoid_f(ldx<AT>(fused, t * ld + off_b + h));
     for (int c = threadIdx.x; c < hd; c += kPrepThreads) {
-      const float z = ldx<AT>(a2, t * hd + c) + dt_bias[c];
-      decay[t * hd + c] = expf(-expf(a_log[c / dim]) * softplus_f(z));
+      const float z = ldx<AT>(a2, t * a2_ld + c) + dt_bias[c];
+      decay[t * hd + c] = expf(-expf(a_log[c / decay_dim]) * softplus_f(z));
     }
     return;
   }
@@ -109,10 +115,10 @@ delta_tails_kernel(const AT* __restrict__ fused, int64_t ld, const int32_t* __re
 
 constexpr int kDsCols = 4, kDsWarps = 8, kDsBlockCols = kDsCols * kDsWarps, kDsStage = 16, kDsThreads = kDsWarps * 32;
 
-template <int DPL>
+template <int DPL, bool DELTA>
 __global__ void __launch_bounds__(kDsThreads)
 delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vn, const float* __restrict__ beta,
-                  const float* __restrict__ decay, const int32_t* __restrict__ positions, const int32_t* __restrict__ seq_start,
+                  const float* __restrict__ decay, int64_t g_row, int g_head, int g_chan, const int32_t* __restrict__ positions, const int32_t* __restrict__ seq_start,
                   const int32_t* __restrict__ seq_slots, float* __restrict__ state, int64_t slot_stride, float* __restrict__ out, int heads,
                   int kv_heads, int dim, int vd) {
   extern __shared__ float stage[];
@@ -133,7 +139,7 @@ delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
 #pragma unroll
     for (int c = 0; c < kDsCols; ++c) Sr[c][i] = (!fresh && d < dim && j0 + c < vd) ? S_st[((int64_t)h * vd + j0 + c) * dim + d] : 0.f;
   }
-  const int qk = kv_heads * dim, hd = heads * dim, hv = heads * vd;
+  const int qk = kv_heads * dim, hv = heads * vd;
   if (n_rows == 1) {
     // a decode row: nothing to stage; the row's inputs are fetched beside the state
     const int64_t t = start;
@@ -151,17 +157,19 @@ delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
       const bool live = d < dim;
       q[i] = live ? qn[t * qk + g * dim + d] : 0.f;
       k[i] = live ? kn[t * qk + g * dim + d] : 0.f;
-      const float gd = live ? decay[t * hd + h * dim + d] : 0.f;
+      const float gd = live ? decay[t * g_row + h * g_head + d * g_chan] : 0.f;
 #pragma unroll
       for (int c = 0; c < kDsCols; ++c) {
         Sr[c][i] *= gd;
-        dot[c] = fmaf(Sr[c][i], k[i], dot[c]);
+        if (DELTA) dot[c] = fmaf(Sr[c][i], k[i], dot[c]);
       }
     }
+    if (DELTA) {
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1)
+      for (int o = 16; o > 0; o >>= 1)
 #pragma unroll
-      for (int c = 0; c < kDsCols; ++c) dot[c] += __shfl_xor_sync(0xffffffffu, dot[c], o);
+        for (int c = 0; c < kDsCols; ++c) dot[c] += __shfl_xor_sync(0xffffffffu, dot[c], o);
+    }
 #pragma unroll
     for (int c = 0; c < kDsCols; ++c) {
       const float u = b * (v[c] - dot[c]);
@@ -208,7 +216,7 @@ delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
       const int64_t t = start + b0 + (live ? r : 0);
       rq[i] = live ? qn[t * qk + g * dim + d] : 0.f;
       rk[i] = live ? kn[t * qk + g * dim + d] : 0.f;
-      rg[i] = live ? decay[t * hd + h * dim + d] : 0.f;
+      rg[i] = live ? decay[t * g_row + h * g_head + d * g_chan] : 0.f;
     }
 #pragma unroll
     for (int i = 0; i < EV; ++i) {
@@ -255,13 +263,15 @@ delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
 #pragma unroll
         for (int c = 0; c < kDsCols; ++c) {
           Sr[c][i] *= gd;
-          dot[c] = fmaf(Sr[c][i], k[i], dot[c]);
+          if (DELTA) dot[c] = fmaf(Sr[c][i], k[i], dot[c]);
         }
       }
+      if (DELTA) {
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1)
+        for (int o = 16; o > 0; o >>= 1)
 #pragma unroll
-        for (int c = 0; c < kDsCols; ++c) dot[c] += __shfl_xor_sync(0xffffffffu, dot[c], o);
+          for (int c = 0; c < kDsCols; ++c) dot[c] += __shfl_xor_sync(0xffffffffu, dot[c], o);
+      }
       const float b = sb[r];
 #pragma unroll
       for (int c = 0; c < kDsCols; ++c) {
@@ -321,25 +331,33 @@ int64_t delta_tail_floats(int heads, int kv_heads, int dim, int vd, int taps) {
 int delta_prep(bool f32, const void* fused, int64_t ld, const void* a2, const float* conv_w, const float* dt_bias, const float* a_log,
                const int32_t* positions, const int32_t* row_to_seq, const int32_t* seq_start, const int32_t* seq_slots, const float* tails,
                int64_t slot_stride, float* qn, float* kn, float* vn, float* beta, float* decay, int T, int heads, int kv_heads, int dim,
-               int vdim, int taps, int decay_rank, int gate_rank, cudaStream_t s) {
+               int vdim, int taps, int decay_rank, int gate_rank, cudaStream_t s, bool head_decay) {
   if (T == 0) return B200_OK;
   B200_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && taps >= 1, B200_ERR_INVALID, "delta_prep: %d heads over %d, %d taps", heads,
                kv_heads, taps);
   B200_REQUIRE(taps == 1 || (tails && seq_slots), B200_ERR_INVALID, "delta_prep: the convolution needs its tails");
   int off[6];
   delta_fused_rows(heads, kv_heads, dim, vdim, decay_rank, gate_rank, off);
+  int64_t a2_ld = (int64_t)heads * dim;
+  int decay_dim = dim;
+  if (head_decay) {   // fused rows q | k | v | gate | b | a without padding: the decay's pre-activation is the row's last group
+    off[5] = 2 * kv_heads * dim + 2 * heads * vdim;
+    a2 = static_cast<const char*>(fused) + (int64_t)(off[5] + heads) * (f32 ? 4 : 2);
+    a2_ld = ld;
+    decay_dim = 1;
+  }
   const size_t smem = (size_t)(2 * kv_heads * dim + heads * vdim) * 4;
   B200_REQUIRE(smem <= 200 * 1024, B200_ERR_UNSUPPORTED, "delta_prep: %zu bytes of channels do not fit shared memory", smem);
   static bool done[2][64] = {};
   if (f32) {
     if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(delta_prep_kernel<float>, 200 * 1024, done[0]));
-    B200_CUDA(launch(delta_prep_kernel<float>, dim3(T, 2), dim3(kPrepThreads), smem, s, (const float*)fused, ld, (const float*)a2, conv_w, dt_bias,
+    B200_CUDA(launch(delta_prep_kernel<float>, dim3(T, 2), dim3(kPrepThreads), smem, s, (const float*)fused, ld, (const float*)a2, a2_ld, decay_dim, conv_w, dt_bias,
                      a_log, positions, row_to_seq, seq_start, seq_slots, tails, slot_stride, qn, kn, vn, beta, decay, heads, kv_heads, dim, vdim,
                      taps, off[5]));
   } else {
     if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(delta_prep_kernel<__nv_bfloat16>, 200 * 1024, done[1]));
     B200_CUDA(launch(delta_prep_kernel<__nv_bfloat16>, dim3(T, 2), dim3(kPrepThreads), smem, s, (const __nv_bfloat16*)fused, ld,
-                     (const __nv_bfloat16*)a2, conv_w, dt_bias, a_log, positions, row_to_seq, seq_start, seq_slots, tails, slot_stride, qn, kn,
+                     (const __nv_bfloat16*)a2, a2_ld, decay_dim, conv_w, dt_bias, a_log, positions, row_to_seq, seq_start, seq_slots, tails, slot_stride, qn, kn,
                      vn, beta, decay, heads, kv_heads, dim, vdim, taps, off[5]));
   }
   return B200_OK;
@@ -361,6 +379,13 @@ int delta_tails(bool f32, const void* fused, int64_t ld, const int32_t* position
 int delta_scan(const float* qn, const float* kn, const float* vn, const float* beta, const float* decay, const int32_t* positions,
                const int32_t* seq_start, const int32_t* seq_slots, float* state, int64_t slot_stride, float* out, int S, int heads,
                int kv_heads, int dim, int vd, cudaStream_t s) {
+  return linear_scan(true, qn, kn, vn, beta, decay, (int64_t)heads * dim, dim, 1, positions, seq_start, seq_slots, state, slot_stride, out, S,
+                     heads, kv_heads, dim, vd, s);
+}
+
+int linear_scan(bool delta_rule, const float* qn, const float* kn, const float* vn, const float* beta, const float* decay, int64_t g_row,
+                int g_head, int g_chan, const int32_t* positions, const int32_t* seq_start, const int32_t* seq_slots, float* state,
+                int64_t slot_stride, float* out, int S, int heads, int kv_heads, int dim, int vd, cudaStream_t s) {
   if (S == 0) return B200_OK;
   B200_REQUIRE(dim > 0 && dim <= 256 && vd > 0, B200_ERR_UNSUPPORTED, "delta_scan: key size %d outside (0, 256]", dim);
   B200_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0, B200_ERR_INVALID, "delta_scan: %d heads over %d", heads, kv_heads);
@@ -368,18 +393,24 @@ int delta_scan(const float* qn, const float* kn, const float* vn, const float* b
   const dim3 grid(S, heads, (vd + kDsBlockCols - 1) / kDsBlockCols), block(kDsThreads);
   const int dpl = (dim + 31) / 32;
   const size_t smem = (size_t)kDsStage * (3 * dim + kDsBlockCols + 1 + kDsWarps * kDsCols * 33) * 4;   // <= 117 KiB
-#define SCAN(D)                                                                                                                       \
+#define SCAN2(D, R)                                                                                                                   \
   do {                                                                                                                                \
     static bool done[64] = {};                                                                                                        \
-    if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(delta_scan_kernel<D>, 128 * 1024, done));                                      \
-    B200_CUDA(launch(delta_scan_kernel<D>, grid, block, smem, s, qn, kn, vn, beta, decay, positions, seq_start, seq_slots, state,     \
-                     slot_stride, out, heads, kv_heads, dim, vd));                                                                    \
+    if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(delta_scan_kernel<D, R>, 128 * 1024, done));                                   \
+    B200_CUDA(launch(delta_scan_kernel<D, R>, grid, block, smem, s, qn, kn, vn, beta, decay, g_row, g_head, g_chan, positions,        \
+                     seq_start, seq_slots, state, slot_stride, out, heads, kv_heads, dim, vd));                                       \
+  } while (0)
+#define SCAN(D)              \
+  do {                       \
+    if (delta_rule) SCAN2(D, true); \
+    else SCAN2(D, false);    \
   } while (0)
   if (dpl <= 1) SCAN(1);
   else if (dpl <= 2) SCAN(2);
   else if (dpl <= 4) SCAN(4);
   else SCAN(8);
 #undef SCAN
+#undef SCAN2
   return B200_OK;
 }
 

@@ -1,0 +1,281 @@
+// Mechanisms of the multi-stream pre-norm layer form (B200_FORM_HYPER) that have no place in the other forms' kernels:
+//  * hyper_step: the residual is n fp32 streams X_1..X_n.  One launch closes a sublayer and opens the next:
+//      close:  X_t = sum_s M[s][t] X_s + mult * b[t] * scale[c] * y        for every t from the OLD streams (M indexed from, to)
+//      open:   u = sum_s a[s] X_s;   h = (u - mean) / sqrt(var + eps) * w + bias      (var = mean of squared deviations)
+//    Streams are elementwise in the channel, so a thread keeps the n values of its channels in registers; only u is
+//    staged (one row in shared memory) for the two statistics passes.  The first launch of a step copies stream 0 (the
+//    scaled embedding) into every stream; the last one runs over the logit rows only, with a = ones and the output norm.
+//    y is an activation row or the sum, in slot order, of n_parts fp32 partial rows (routed experts).
+//  * qkv_rotate_cache: plain q | k | v projections; the leading rot_dims dimensions of every q and k head turn by the
+//    angles of an fp32 cos|sin table, dimension i paired with i + rot_dims / 2 (half layout) or 2i with 2i + 1; q leaves
+//    as fp32 rows, k and v go to the paged caches.
+//  * polynorm: p(z) = c0 N(z) + c1 N(z^2) + c2 N(z^3) + c3 over the ff entries of a token, N(v) = v / sqrt(mean(v^2) + eps);
+//    the three mean squares come from one pass over the row (z^2, z^4, z^6), all in fp32.
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+template <typename AT> __device__ __forceinline__ float ldx(const AT* p, int64_t i);
+template <> __device__ __forceinline__ float ldx<float>(const float* p, int64_t i) { return p[i]; }
+template <> __device__ __forceinline__ float ldx<__nv_bfloat16>(const __nv_bfloat16* p, int64_t i) { return __bfloat162float(p[i]); }
+template <typename AT> __device__ __forceinline__ void stx(AT* p, int64_t i, float v);
+template <> __device__ __forceinline__ void stx<float>(float* p, int64_t i, float v) { p[i] = v; }
+template <> __device__ __forceinline__ void stx<__nv_bfloat16>(__nv_bfloat16* p, int64_t i, float v) { p[i] = __float2bfloat16_rn(v); }
+
+constexpr int kHyThreads = 256;
+constexpr int kMaxN = B200_MAX_STREAMS;
+
+__device__ __forceinline__ float block_sum_hy(float v, float* red) {
+  v = warp_sum(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float a = 0.f;
+#pragma unroll
+  for (int i = 0; i < kHyThreads / 32; ++i) a += red[i];
+  return a;
+}
+
+template <typename AT, int N>
+__global__ void __launch_bounds__(kHyThreads)
+hyper_step_kernel(float* X, int64_t sstride, int init, const AT* __restrict__ y, const float* __restrict__ parts, int n_parts,
+                  const float* __restrict__ scale, const float* __restrict__ hc, float mult, const float* __restrict__ open_in,
+                  const float* __restrict__ nw, const float* __restrict__ nb, float eps, const int32_t* __restrict__ rows,
+                  float* __restrict__ h_f32, AT* __restrict__ h_act, float* __restrict__ sum_out, int width) {
+  extern __shared__ float hy_row[];
+  __shared__ float red[kHyThreads / 32];
+  __shared__ float coef[2 * kMaxN + kMaxN * kMaxN + kMaxN];   // a | b | M of the closing sublayer, then the opening a
+  pdl_wait();
+  pdl_launch_dependents();
+  const int64_t t = blockIdx.x;
+  const int64_t src = rows ? (int64_t)rows[t] : t;
+  if (threadIdx.x < 2 * N + N * N) coef[threadIdx.x] = hc ? hc[threadIdx.x] : 0.f;
+  if (threadIdx.x < N) coef[2 * N + N * N + threadIdx.x] = open_in ? open_in[threadIdx.x] : 1.0f;
+  __syncthreads();
+  const float* cb = coef + N;
+  const float* cm = coef + 2 * N;
+  const float* ca = coef + 2 * N + N * N;
+  float sum = 0.f;
+  for (int c = threadIdx.x; c < width; c += kHyThreads) {
+    float xs[N], xn[N];
+#pragma unroll
+    for (int s = 0; s < N; ++s) xs[s] = X[(init ? 0 : s) * sstride + src * width + c];
+    if (hc) {
+      float yv;
+      if (y) {
+        yv = ldx<AT>(y, src * width + c);
+      } else {
+        yv = 0.f;
+        for (int j = 0; j < n_parts; ++j) yv += parts[(src * n_parts + j) * width + c];
+      }
+      yv = yv * scale[c] * mult;
+#pragma unroll
+      for (int q = 0; q < N; ++q) {
+        float a = 0.f;
+#pragma unroll
+        for (int s = 0; s < N; ++s) a = fmaf(cm[s * N + q], xs[s], a);
+        xn[q] = fmaf(cb[q], yv, a);
+      }
+      if (!rows) {
+#pragma unroll
+        for (int q = 0; q < N; ++q) X[q * sstride + src * width + c] = xn[q];
+      }
+    } else {
+#pragma unroll
+      for (int q = 0; q < N; ++q) xn[q] = xs[q];
+      if (init && !rows) {
+#pragma unroll
+        for (int q = 1; q < N; ++q) X[q * sstride + src * width + c] = xn[q];
+      }
+    }
+    float u = 0.f, all = 0.f;
+#pragma unroll
+    for (int q = 0; q < N; ++q) {
+      u = fmaf(ca[q], xn[q], u);
+      all += xn[q];
+    }
+    if (sum_out) sum_out[t * width + c] = all;
+    hy_row[c] = u;
+    sum += u;
+  }
+  if (!h_f32 && !h_act) return;
+  if (!nw) {
+    __syncthreads();
+    for (int c = threadIdx.x; c < width; c += kHyThreads) {
+      if (h_f32) h_f32[t * width + c] = hy_row[c];
+      if (h_act) stx<AT>(h_act, t * width + c, hy_row[c]);
+    }
+    return;
+  }
+  const float mean = block_sum_hy(sum, red) / (float)width;
+  float sq = 0.f;
+  for (int c = threadIdx.x; c < width; c += kHyThreads) {
+    const float d = hy_row[c] - mean;
+    sq = fmaf(d, d, sq);
+  }
+  const float rstd = 1.0f / sqrtf(block_sum_hy(sq, red) / (float)width + eps);
+  for (int c = threadIdx.x; c < width; c += kHyThreads) {
+    const float v = (hy_row[c] - mean) * rstd * nw[c] + (nb ? nb[c] : 0.f);
+    if (h_f32) h_f32[t * width + c] = v;
+    if (h_act) stx<AT>(h_act, t * width + c, v);
+  }
+}
+
+// one CTA per row; a warp takes head vectors round robin (query heads, key heads, value heads)
+template <typename AT, typename CT>
+__global__ void __launch_bounds__(256)
+qkv_rotate_cache_kernel(const AT* __restrict__ qkv, int64_t ld, const int32_t* __restrict__ positions, const int32_t* __restrict__ slots,
+                        const float* __restrict__ rot, int rot_dims, int half_layout, int64_t max_pos, float* __restrict__ qout,
+                        CT* __restrict__ kc, CT* __restrict__ vc, int heads, int kv_heads, int dim, int vdim, int block_size) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int64_t t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int pos = positions[t];
+  pos = pos < 0 ? 0 : (pos >= max_pos ? (int)max_pos - 1 : pos);
+  const int half = rot ? rot_dims >> 1 : 0;
+  const float* cs = rot ? rot + (int64_t)pos * 2 * half : nullptr;
+  const int slot = slots[t];
+  const int64_t blk = slot >= 0 ? slot / block_size : 0, off = slot >= 0 ? slot % block_size : 0;
+  const int nqk = heads + kv_heads;
+  for (int v = warp; v < nqk + kv_heads; v += 8) {
+    if (v >= nqk) {   // a value head: copied
+      if (slot < 0) continue;
+      const int g = v - nqk;
+      const AT* src = qkv + t * ld + (int64_t)nqk * dim + (int64_t)g * vdim;
+      CT* dst = vc + ((blk * kv_heads + g) * block_size + off) * vdim;
+      for (int i = lane; i < vdim; i += 32) stx<CT>(dst, i, ldx<AT>(src, i));
+      continue;
+    }
+    const bool is_q = v < heads;
+    const int g = is_q ? v : v - heads;
+    if (!is_q && slot < 0) continue;
+    const AT* src = qkv + t * ld + (int64_t)v * dim;
+    float* qd = qout + (t * heads + g) * dim;
+    CT* kd = kc + ((blk * kv_heads + g) * block_size + off) * dim;
+    for (int i = lane; i < half; i += 32) {   // the pairs that turn
+      const int i0 = half_layout ? i : 2 * i, i1 = half_layout ? i + half : 2 * i + 1;
+      const float a = ldx<AT>(src, i0), b = ldx<AT>(src, i1), c = cs[i], sn = cs[half + i];
+      const float o0 = fmaf(a, c, -b * sn), o1 = fmaf(b, c, a * sn);
+      if (is_q) {
+        qd[i0] = o0;
+        qd[i1] = o1;
+      } else {
+        stx<CT>(kd, i0, o0);
+        stx<CT>(kd, i1, o1);
+      }
+    }
+    for (int i = 2 * half + lane; i < dim; i += 32) {   // the rest passes
+      const float a = ldx<AT>(src, i);
+      if (is_q) qd[i] = a;
+      else stx<CT>(kd, i, a);
+    }
+  }
+}
+
+template <typename AT>
+__global__ void __launch_bounds__(kHyThreads)
+polynorm_kernel(const AT* __restrict__ z, const float* __restrict__ coef, AT* __restrict__ out, int ff, float eps) {
+  extern __shared__ float pz[];
+  __shared__ float red[kHyThreads / 32];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int64_t t = blockIdx.x;
+  float s2 = 0.f, s4 = 0.f, s6 = 0.f;
+  for (int c = threadIdx.x; c < ff; c += kHyThreads) {
+    const float v = ldx<AT>(z, t * ff + c), v2 = v * v, v3 = v2 * v;
+    pz[c] = v;
+    s2 += v2;
+    s4 = fmaf(v2, v2, s4);
+    s6 = fmaf(v3, v3, s6);
+  }
+  const float r1 = 1.0f / sqrtf(block_sum_hy(s2, red) / (float)ff + eps);
+  const float r2 = 1.0f / sqrtf(block_sum_hy(s4, red) / (float)ff + eps);
+  const float r3 = 1.0f / sqrtf(block_sum_hy(s6, red) / (float)ff + eps);
+  const float c0 = coef[0] * r1, c1 = coef[1] * r2, c2 = coef[2] * r3, c3 = coef[3];
+  for (int c = threadIdx.x; c < ff; c += kHyThreads) {
+    const float v = pz[c], v2 = v * v;
+    stx<AT>(out, t * ff + c, fmaf(c0, v, fmaf(c1, v2, fmaf(c2, v2 * v, c3))));
+  }
+}
+
+template <typename AT, int N>
+int hyper_step_n(float* X, int64_t sstride, int init, const void* y, const float* parts, int n_parts, const float* scale, const float* hc,
+                 float mult, const float* open_in, const float* nw, const float* nb, float eps, const int32_t* rows, float* h_f32, void* h_act,
+                 float* sum_out, int R, int width, cudaStream_t s) {
+  const size_t smem = (size_t)width * 4;
+  static bool done[64] = {};
+  if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(hyper_step_kernel<AT, N>, 200 * 1024, done));
+  B200_CUDA(launch(hyper_step_kernel<AT, N>, dim3(R), dim3(kHyThreads), smem, s, X, sstride, init, (const AT*)y, parts, n_parts, scale, hc, mult,
+                   open_in, nw, nb, eps, rows, h_f32, (AT*)h_act, sum_out, width));
+  return B200_OK;
+}
+
+template <typename AT>
+int hyper_step_t(int n, float* X, int64_t sstride, int init, const void* y, const float* parts, int n_parts, const float* scale, const float* hc,
+                 float mult, const float* open_in, const float* nw, const float* nb, float eps, const int32_t* rows, float* h_f32, void* h_act,
+                 float* sum_out, int R, int width, cudaStream_t s) {
+#define HY(N) \
+  case N: return hyper_step_n<AT, N>(X, sstride, init, y, parts, n_parts, scale, hc, mult, open_in, nw, nb, eps, rows, h_f32, h_act, sum_out, R, width, s)
+  switch (n) {
+    HY(1);
+    HY(2);
+    HY(3);
+    HY(4);
+    HY(5);
+    HY(6);
+    HY(7);
+    HY(8);
+  }
+#undef HY
+  return B200_ERR_UNSUPPORTED;
+}
+
+}  // namespace
+
+int hyper_step(bool f32, float* X, int64_t sstride, int n, bool init, const void* y, const float* parts, int n_parts, const float* scale,
+               const float* hc, float mult, const float* open_in, const float* nw, const float* nb, float eps, const int32_t* rows,
+               float* h_f32, void* h_act, float* sum_out, int R, int width, cudaStream_t s) {
+  if (R == 0) return B200_OK;
+  B200_REQUIRE(X && n >= 1 && n <= kMaxN, B200_ERR_INVALID, "hyper_step: %d streams outside [1, %d]", n, kMaxN);
+  B200_REQUIRE(!hc || ((y || (parts && n_parts > 0)) && scale), B200_ERR_INVALID, "hyper_step: a closing sublayer needs its result and its scale");
+  B200_REQUIRE((size_t)width * 4 <= 200 * 1024, B200_ERR_UNSUPPORTED, "hyper_step: width %d does not fit shared memory", width);
+  return f32 ? hyper_step_t<float>(n, X, sstride, init ? 1 : 0, y, parts, n_parts, scale, hc, mult, open_in, nw, nb, eps, rows, h_f32, h_act,
+                                   sum_out, R, width, s)
+             : hyper_step_t<__nv_bfloat16>(n, X, sstride, init ? 1 : 0, y, parts, n_parts, scale, hc, mult, open_in, nw, nb, eps, rows, h_f32,
+                                           h_act, sum_out, R, width, s);
+}
+
+int qkv_rotate_cache(bool f32, const void* qkv, int64_t ld, const int32_t* positions, const int32_t* slots, const float* rot, int rot_dims,
+                     bool half_layout, int64_t max_pos, float* qout, void* kc, void* vc, int T, int heads, int kv_heads, int dim, int vdim,
+                     int block_size, cudaStream_t s) {
+  if (T == 0) return B200_OK;
+  B200_REQUIRE(rot_dims % 2 == 0 && rot_dims <= dim && rot_dims >= 0, B200_ERR_UNSUPPORTED, "qkv_rotate_cache: %d rotated dimensions in heads of %d",
+               rot_dims, dim);
+  if (f32)
+    B200_CUDA(launch(qkv_rotate_cache_kernel<float, float>, dim3(T), dim3(256), (size_t)0, s, (const float*)qkv, ld, positions, slots, rot,
+                     rot ? rot_dims : 0, half_layout ? 1 : 0, max_pos, qout, (float*)kc, (float*)vc, heads, kv_heads, dim, vdim, block_size));
+  else
+    B200_CUDA(launch(qkv_rotate_cache_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(T), dim3(256), (size_t)0, s, (const __nv_bfloat16*)qkv, ld,
+                     positions, slots, rot, rot ? rot_dims : 0, half_layout ? 1 : 0, max_pos, qout, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, heads,
+                     kv_heads, dim, vdim, block_size));
+  return B200_OK;
+}
+
+int polynorm(bool f32, const void* z, const float* coef, void* out, int T, int ff, float eps, cudaStream_t s) {
+  if (T == 0) return B200_OK;
+  const size_t smem = (size_t)ff * 4;
+  B200_REQUIRE(smem <= 200 * 1024, B200_ERR_UNSUPPORTED, "polynorm: %d entries do not fit shared memory", ff);
+  static bool done[2][64] = {};
+  if (f32) {
+    if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(polynorm_kernel<float>, 200 * 1024, done[0]));
+    B200_CUDA(launch(polynorm_kernel<float>, dim3(T), dim3(kHyThreads), smem, s, (const float*)z, coef, (float*)out, ff, eps));
+  } else {
+    if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(polynorm_kernel<__nv_bfloat16>, 200 * 1024, done[1]));
+    B200_CUDA(launch(polynorm_kernel<__nv_bfloat16>, dim3(T), dim3(kHyThreads), smem, s, (const __nv_bfloat16*)z, coef, (__nv_bfloat16*)out, ff, eps));
+  }
+  return B200_OK;
+}
+
+}  // namespace b200

@@ -16,7 +16,7 @@
 //    from one row to the next.
 //    n and m are kept once per CTA (every CTA of a head needs them from the step before, so they cannot share one copy
 //    that one of them overwrites).  A sequence whose first row is at position 0 starts from zeros.
-//  * head_norm_gate: unit RMS per head, weight, sigmoid gate.
+//  * head_norm_gate: unit RMS per head, weight, sigmoid gate (or the gate's silu).
 #include "common.cuh"
 
 namespace b200 {
@@ -287,7 +287,7 @@ mlstm_scan_kernel(const AT* __restrict__ qkv, int64_t ld, int q_off, int k_off, 
 template <typename AT>
 __global__ void __launch_bounds__(128)
 head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ w, const AT* __restrict__ gate, int64_t ldg,
-                      AT* __restrict__ out, int heads, int vd, float eps) {
+                      AT* __restrict__ out, int heads, int vd, float eps, int gate_silu) {
   pdl_wait();
   pdl_launch_dependents();
   const int64_t t = blockIdx.x;
@@ -301,7 +301,10 @@ head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ w, 
     for (int j = lane; j < vd; j += 32) {
       float v = src[j] * inv;
       if (w) v *= w[h * vd + j];
-      if (gate) v *= 1.0f / (1.0f + expf(-ldx<AT>(gate, t * ldg + h * vd + j)));
+      if (gate) {
+        const float gz = ldx<AT>(gate, t * ldg + h * vd + j);
+        v *= (gate_silu ? gz : 1.0f) / (1.0f + expf(-gz));
+      }
       stx<AT>(out, (t * heads + h) * vd + j, v);
     }
   }
@@ -377,14 +380,14 @@ int mlstm_scan(bool f32, const void* qkv, int64_t ld, int q_off, int k_off, int 
 }
 
 int head_norm_gate(bool f32, const float* o, const float* w, const void* gate, int64_t ldg, void* out, int T, int heads, int vd, float eps,
-                   cudaStream_t s) {
+                   cudaStream_t s, bool gate_silu) {
   if (T == 0) return B200_OK;
   if (f32)
     B200_CUDA(launch(head_norm_gate_kernel<float>, dim3(T), dim3(128), (size_t)0, s, o, w, (const float*)gate, ldg, (float*)out, heads, vd,
-                     eps));
+                     eps, gate_silu ? 1 : 0));
   else
     B200_CUDA(launch(head_norm_gate_kernel<__nv_bfloat16>, dim3(T), dim3(128), (size_t)0, s, o, w, (const __nv_bfloat16*)gate, ldg,
-                     (__nv_bfloat16*)out, heads, vd, eps));
+                     (__nv_bfloat16*)out, heads, vd, eps, gate_silu ? 1 : 0));
   return B200_OK;
 }
 

@@ -14,6 +14,8 @@
 //  * tensor-core form (bf16 serving mode, width and ff multiples of 8; every step size): the (token, slot) pairs are
 //    grouped by expert into whole token tiles, the token rows gathered, and two launches of the grouped tcgen05 linear
 //    (gemm_tc.cu) run gate|up and down for all experts at once; the second one scatters the weighted fp32 rows.
+// Score mode 2 (chosen-softmax router): the bias is part of the logits, the `top` largest logits win and the mixing weights are
+// the softmax over those `top` logits alone.  Experts may also be gated by B200_ACT_SWIGLU_CLAMP (gate_combine, common.cuh).
 // All write one fp32 partial row per (token, slot), already multiplied by the mixing weight; the consumer (the norm that
 // follows the feed-forward) adds the slots in slot order, so the result does not depend on which form ran or on what else
 // was in the step beyond fp32 rounding.
@@ -49,7 +51,13 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
 __device__ __forceinline__ void route_select(float* sc, float* ch, float* gs, const float* __restrict__ bias, int lane, int t,
                                              int experts, int top, int groups, int keep, int32_t* __restrict__ out_ids,
                                              float* __restrict__ out_w, int sigmoid_scores) {
-  if (sigmoid_scores) {   // every expert scored on its own
+  if (sigmoid_scores == 2) {   // the logits themselves compete; the weights follow the choice
+    for (int e = lane; e < experts; e += 32) {
+      const float z = sc[e] + (bias ? bias[e] : 0.f);
+      sc[e] = z;
+      ch[e] = z;
+    }
+  } else if (sigmoid_scores) {   // every expert scored on its own
     for (int e = lane; e < experts; e += 32) {
       const float s = 1.0f / (1.0f + expf(-sc[e]));
       sc[e] = s;
@@ -120,6 +128,17 @@ __device__ __forceinline__ void route_select(float* sc, float* ch, float* gs, co
       if (bi != 0x7fffffff) ch[e] = __int_as_float(0x7fc00000);
     }
     __syncwarp();
+  }
+  if (sigmoid_scores == 2 && lane == 0) {   // softmax over the chosen logits (the first one is the largest)
+    float* w = out_w + (int64_t)t * top;
+    const float mx = w[0];
+    float sum = 0.f;
+    for (int k = 0; k < top; ++k) {
+      w[k] = expf(w[k] - mx);
+      sum += w[k];
+    }
+    const float inv = 1.0f / sum;
+    for (int k = 0; k < top; ++k) w[k] *= inv;
   }
 }
 
@@ -207,7 +226,7 @@ moe_expert_rows_kernel(const AT* __restrict__ x, const __nv_bfloat16* __restrict
       b = 1.0f;
     }
     a = warp_sum(a);
-    if (lane == 0) as[f] = act_apply(a, form.act) * b;
+    if (lane == 0) as[f] = form.gated ? gate_combine(a, b, form.act, form.limit) : act_apply(a, form.act);
   }
   __syncthreads();
   const __nv_bfloat16* wd = w_down + (int64_t)e * width * ff;
@@ -298,7 +317,7 @@ moe_expert_grouped_kernel(const AT* __restrict__ x, const __nv_bfloat16* __restr
 #pragma unroll
     for (int r = 0; r < kGrpTokens; ++r) {
       const float av = warp_sum(a[r]), bv = warp_sum(b[r]);
-      if (lane == 0) as[r * ff + f] = act_apply(av, form.act) * (form.gated ? bv : 1.0f);
+      if (lane == 0) as[r * ff + f] = form.gated ? gate_combine(av, bv, form.act, form.limit) : act_apply(av, form.act);
     }
   }
   __syncthreads();
@@ -498,7 +517,7 @@ static int moe_experts_tc(const __nv_bfloat16* x, const __nv_bfloat16* w_gu, con
   } else if (form.act != B200_ACT_SILU) {
     rc = linear_tc_grouped(xg, width, N, n_tiles, w_gu, experts, 2 * ff, width, tile_expert, gu, 2 * ff, nullptr, nullptr, nullptr, s);
     if (rc) return rc;
-    rc = ff_act(false, gu, act, (int)rows, ff, true, form.act, s);
+    rc = ff_act(false, gu, act, (int)rows, ff, true, form.act, s, form.limit);
     if (rc) return rc;
   } else if (fuse_env && ff % 64 == 0 && (N <= 64 || fuse_env > 1)) {
     // gate and up rows of a slab come in as two 64-row boxes; the epilogue activates (as the dense gate|up linear does).
@@ -517,8 +536,8 @@ static int moe_experts_tc(const __nv_bfloat16* x, const __nv_bfloat16* w_gu, con
 
 int moe_route(bool f32, const void* x, const __nv_bfloat16* w_router, const float* bias, int T, int width, int experts, int top,
               int groups, int keep, int32_t* out_ids, float* out_w, cudaStream_t s, float* logits_ws, void* lin_ws,
-              int64_t lin_ws_bytes, bool sigmoid_scores) {
-  const int sg = sigmoid_scores ? 1 : 0;
+              int64_t lin_ws_bytes, int score_mode) {
+  const int sg = score_mode;
   if (T == 0) return B200_OK;
   B200_REQUIRE(experts > 0 && top > 0 && top <= experts, B200_ERR_INVALID, "router: top %d of %d experts", top, experts);
   if (groups < 1) groups = 1;

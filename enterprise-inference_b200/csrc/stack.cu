@@ -29,6 +29,19 @@
 //     delta:     fused q | k | v | a1 | g1 | b -> W_a2, W_g2 -> convolution, unit vectors, beta, decays -> recurrence over the
 //                state slot -> unit RMS per head, weight, gate -> W_o
 //   logit rows: LN(x[rows]) * w + b -> W_head -> fp32 logits and their bf16 copy -> argmax
+//
+// Multi-stream pre-norm form (b200_stack_cfg.form = B200_FORM_HYPER), same step entry, cache, state slots and graph replay:
+//   X_1..X_n = table[id] * embed_scale                                    n fp32 residual streams
+//   per sublayer (mixer, then the feed-forward where the layer has one):
+//     hyper_step: closes the sublayer before (X_t = sum_s M[s][t] X_s + mult b[t] scale y) and opens this one (u = sum_s a[s] X_s,
+//                 h = LN(u) w + bias, fp32)  ->  canon_conv: h + conv(h) (tail in the state slot)  ->  the sublayer
+//     attention:  fused q | k | v -> half-layout rotation, k and v into the paged cache -> attention with a learned sink -> W_o
+//     delta:      fused q | k | v | gate | b | a -> convolution, unit vectors, beta, one decay per head -> recurrence -> unit RMS,
+//                 weight, silu gate -> W_o
+//     ssd:        fused z | x | B | C | dt -> convolution with bias, step sizes and decays -> recurrence without the correction
+//                 term -> skip, gate, grouped RMS norm -> W_o
+//     dense:      W_up -> polynomial of unit-RMS powers -> W_down;   experts: chosen-softmax router, clamped gated experts
+//   logit rows: hyper_step over the rows (closes the last sublayer, a = ones, output norm) -> W_head -> fp32 logits -> argmax
 #include <math.h>
 #include <stdlib.h>
 
@@ -55,6 +68,10 @@ struct StackLayerW {
               *decay_log = nullptr;
   const __nv_bfloat16 *uq = nullptr, *decay_up = nullptr, *gate_up = nullptr;
   bool gu_interleaved = false;   // mlp_gate_up holds 128-row slabs of 64 gate rows + the 64 matching up rows
+  // multi-stream form
+  const float *n_mix_pre_b = nullptr, *n_mlp_pre_b = nullptr, *scale_mix = nullptr, *scale_mlp = nullptr, *hc_mix = nullptr, *hc_mlp = nullptr,
+              *canon_mlp = nullptr, *conv_b = nullptr, *skip = nullptr, *mlp_act = nullptr;
+  int64_t tail2_off = 0, ctail_off = 0;   // floats from the start of a state slot: the feed-forward's input convolution tail, the mixer's own
 };
 
 struct StackModel {
@@ -95,6 +112,8 @@ struct StackModel {
   void *cq = nullptr, *qh = nullptr, *a2 = nullptr, *g2 = nullptr;   // query latent, queries, decay and gate projections
   float *dq = nullptr, *dk = nullptr, *dv = nullptr, *dbeta = nullptr, *ddecay = nullptr;   // what the recurrence reads
   float* zero_sink = nullptr;          // [heads] zeros: a sink of score 0 is one more unit in the denominator
+  // multi-stream form
+  float* xs = nullptr;                 // [streams][max_tokens][width]
 };
 
 bool paged_attn_tc_supported(int hq, int hkv, int block_size);   // attn_tc.cu
@@ -102,6 +121,8 @@ bool paged_attn_tc_supported(int hq, int hkv, int block_size);   // attn_tc.cu
 static bool is_latent(const b200_stack_layer& L) { return L.mixer == B200_MIXER_LATENT; }
 static bool is_mlstm(const b200_stack_layer& L) { return L.mixer == B200_MIXER_MLSTM; }
 static bool is_delta(const b200_stack_layer& L) { return L.mixer == B200_MIXER_DELTA; }
+static bool is_ssd(const b200_stack_layer& L) { return L.mixer == B200_MIXER_SSD; }
+static bool head_decay(const b200_stack_layer& L) { return (L.mixer_flags & B200_MIXF_HEAD_DECAY) != 0; }
 
 // bf16 mode, keys and values of 64 to 128 dimensions in blocks of 128 tokens: the tcgen05 attention kernels of the fixed
 // decoder stack serve the layer.  They are built for 128-wide heads, so the layer's cache rows and its bf16 queries are
@@ -115,11 +136,11 @@ static bool layer_attn_tc(const b200_stack_cfg& m, const b200_stack_layer& L) {
 // latent mixers cache one row [latent | rotated key part] per token (no value cache); mLSTM layers cache nothing
 static int cache_kdim(const b200_stack_cfg& m, const b200_stack_layer& L) {
   if (is_latent(L)) return L.kv_share > 0 ? 0 : L.kv_rank + L.rot_dim;
-  if (is_mlstm(L) || is_delta(L)) return 0;
+  if (is_mlstm(L) || is_delta(L) || is_ssd(L)) return 0;
   return layer_attn_tc(m, L) ? kHeadDim : L.dim;
 }
 static int cache_vdim(const b200_stack_cfg& m, const b200_stack_layer& L) {
-  if (is_latent(L) || is_mlstm(L) || is_delta(L)) return 0;
+  if (is_latent(L) || is_mlstm(L) || is_delta(L) || is_ssd(L)) return 0;
   return layer_attn_tc(m, L) ? kHeadDim : L.vdim;
 }
 
@@ -127,6 +148,8 @@ static int64_t up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
 
 // rows of the fused projection of the mixer's input
 static int qkv_rows(const b200_stack_layer& L) {
+  if (is_ssd(L)) return 2 * L.heads * L.vdim + 2 * L.kv_heads * L.dim + L.heads;             // z | x | B | C | dt
+  if (is_delta(L) && head_decay(L)) return 2 * L.kv_heads * L.dim + 2 * L.heads * L.vdim + 2 * L.heads;   // q | k | v | gate | b | a
   if (is_delta(L)) return delta_fused_rows(L.heads, L.kv_heads, L.dim, L.vdim, L.decay_rank, L.gate_rank, nullptr);
   if (is_latent(L) && L.q_rank > 0)   // query latent | key/value latent (unless another layer's is read) | one gate row per head
     return L.q_rank + (L.kv_share > 0 ? 0 : L.kv_rank) + ((L.mixer_flags & B200_MIXF_HEAD_GATE) ? L.heads : 0);
@@ -229,11 +252,44 @@ static int stack_ready_postnorm(const b200_ctx* c) {
   return B200_OK;
 }
 
+static int stack_ready_hyper(const b200_ctx* c) {
+  const StackModel* M = c->stack;
+  const b200_stack_cfg& m = M->cfg;
+  B200_REQUIRE(M->final_norm_b, B200_ERR_STATE, "step: the output norm's bias is not set");
+  B200_REQUIRE(m.n_state_slots <= 0 || M->state, B200_ERR_STATE, "step: state slots not set");
+  for (size_t l = 0; l < M->layers.size(); ++l) {
+    const b200_stack_layer& L = M->layers[l];
+    const StackLayerW& W = M->w[l];
+    const int li = (int)l;
+    B200_REQUIRE(W.n_mix_pre && W.n_mix_pre_b && W.scale_mix && W.hc_mix && W.qkv && W.o, B200_ERR_STATE, "step: layer %d mixer weights incomplete", li);
+    B200_REQUIRE(m.canon_taps <= 0 || W.canon, B200_ERR_STATE, "step: layer %d convolution weights missing", li);
+    if (L.mixer == B200_MIXER_ATTENTION) {
+      B200_REQUIRE(W.kc && W.vc, B200_ERR_STATE, "step: layer %d cache missing", li);
+      B200_REQUIRE(!(L.mixer_flags & B200_MIXF_SINK) || W.sink, B200_ERR_STATE, "step: layer %d sink missing", li);
+      B200_REQUIRE(L.rot_dims == 0 || (L.rot_table >= 0 && M->rot[L.rot_table] && M->rot_half[L.rot_table] * 2 == L.rot_dims),
+                   B200_ERR_STATE, "step: layer %d rotation table missing or of another size", li);
+    } else if (is_delta(L)) {
+      B200_REQUIRE(W.conv && W.decay_bias && W.decay_log && W.head_norm, B200_ERR_STATE, "step: layer %d recurrent weights incomplete", li);
+    } else {
+      B200_REQUIRE(W.conv && W.decay_bias && W.decay_log && W.head_norm && W.skip, B200_ERR_STATE, "step: layer %d recurrent weights incomplete", li);
+    }
+    if (L.mlp != B200_MLP_NONE) {
+      B200_REQUIRE(W.n_mlp_pre && W.n_mlp_pre_b && W.scale_mlp && W.hc_mlp, B200_ERR_STATE, "step: layer %d feed-forward norm / stream weights missing", li);
+      B200_REQUIRE(m.canon_taps <= 0 || W.canon_mlp, B200_ERR_STATE, "step: layer %d feed-forward convolution weights missing", li);
+    }
+    if (L.mlp == B200_MLP_DENSE)
+      B200_REQUIRE(W.mlp_gate_up && W.mlp_down && (L.act != B200_ACT_POLYNORM || W.mlp_act), B200_ERR_STATE, "step: layer %d feed-forward weights incomplete", li);
+    if (L.mlp == B200_MLP_MOE) B200_REQUIRE(W.router && W.e_gate_up && W.e_down, B200_ERR_STATE, "step: layer %d expert weights incomplete", li);
+  }
+  return B200_OK;
+}
+
 int stack_ready(const b200_ctx* c) {
   const StackModel* M = c->stack;
   B200_REQUIRE(M->embed && M->head && M->final_norm, B200_ERR_STATE, "step: embedding / output weights not set");
   if (M->cfg.form == B200_FORM_PARALLEL) return stack_ready_parallel(c);
   if (M->cfg.form == B200_FORM_POSTNORM) return stack_ready_postnorm(c);
+  if (M->cfg.form == B200_FORM_HYPER) return stack_ready_hyper(c);
   for (size_t l = 0; l < M->layers.size(); ++l) {
     const b200_stack_layer& L = M->layers[l];
     const StackLayerW& W = M->w[l];
@@ -531,11 +587,145 @@ static int stack_enqueue_step_parallel(b200_ctx* c, const StepArgs& a, cudaStrea
   return B200_OK;
 }
 
+// The step of the multi-stream pre-norm form.
+static int stack_enqueue_step_hyper(b200_ctx* c, const StepArgs& a, cudaStream_t s) {
+  StackModel* M = c->stack;
+  const b200_stack_cfg& m = M->cfg;
+  const bool f32 = m.f32 != 0;
+  const int T = a.T, Wd = m.width, nL = m.n_layers, n = m.streams;
+  const int64_t es = M->esz;
+  int rc;
+#define STEP(expr)     \
+  do {                 \
+    rc = (expr);       \
+    if (rc) return rc; \
+  } while (0)
+  const bool stateful = m.n_state_slots > 0;
+  const int S = a.n_seqs > 0 ? a.n_seqs : T;
+  const int32_t* seq_slots = a.seq_slots;
+  B200_REQUIRE(!stateful || seq_slots, B200_ERR_STATE, "step: the state slots of the step's sequences were not given");
+  B200_REQUIRE(S <= T, B200_ERR_INVALID, "step: %d sequences in %d rows", S, T);
+  int attn_plan = (a.row_to_seq && T >= 32 && T >= 2 * S) ? 1 : 0;
+  static const int plan_env = getenv("B200_STACK_ATTN_RUNS") ? atoi(getenv("B200_STACK_ATTN_RUNS")) : 1;
+  if (!plan_env) attn_plan = 0;
+  bool runs_built = false;   // the step's run list is in the attention workspace
+  auto step_runs = [&](bool& built) -> int {
+    if (built) return B200_OK;
+    built = true;
+    return paged_attn_runs_plan(a.row_to_seq, a.ctx_lens, T, M->attn_ws, s);
+  };
+  const int64_t sstride = (int64_t)m.max_tokens * Wd;
+  const bool conv = m.canon_taps >= 1;
+  float* X = M->xs;
+  if (stateful) STEP(seq_bounds(a.row_to_seq, T, S, M->seq_start, s));
+  STEP(embed_scaled(a.ids, M->embed, X, T, Wd, m.vocab, m.embed_scale, s, a.prev_tokens, a.n_prev));
+  // what the sublayer before left to be closed: its result (an activation row or expert partial rows), scale and coefficients
+  const void* y_prev = nullptr;
+  const float *parts_prev = nullptr, *scale_prev = nullptr, *hc_prev = nullptr;
+  int n_parts_prev = 0;
+  bool first = true;
+  // closes the sublayer before, opens one with coefficients hc / norm (w, b) / convolution cw (tail at tail_off) into `out`
+  auto open = [&](const float* hc, const float* w, const float* b, const float* cw, int64_t tail_off, void* out, float* tap) -> int {
+    int r = hyper_step(f32, X, sstride, n, first, y_prev, parts_prev, n_parts_prev, scale_prev, hc_prev, m.residual_mult, hc, w, b, m.norm_eps,
+                       nullptr, conv ? M->h1f : nullptr, conv ? nullptr : out, tap, T, Wd, s);
+    first = false;
+    if (r || !conv) return r;
+    return canon_conv(f32, M->h1f, cw, out, T, Wd, m.canon_taps, a.positions, a.row_to_seq, M->seq_start, seq_slots,
+                      M->state ? M->state + tail_off : nullptr, M->slot_floats, s);
+  };
+  for (int l = 0; l < nL; ++l) {
+    const b200_stack_layer& L = M->layers[l];
+    const StackLayerW& W = M->w[l];
+    const int qr = qkv_rows(L), av = L.heads * L.vdim;
+    float* tap = (M->tap && l > 0) ? M->tap + (int64_t)(l - 1) * T * Wd : nullptr;   // the layer before is complete once its last sublayer is closed
+    STEP(open(W.hc_mix, W.n_mix_pre, W.n_mix_pre_b, W.canon, W.tail_off, M->hc, tap));
+    STEP(stack_linear(c, M->hc, Wd, W.qkv, M->qkv, qr, T, qr, Wd, s));
+    if (L.mixer == B200_MIXER_ATTENTION) {
+      const float* rot = L.rot_dims > 0 ? M->rot[L.rot_table] : nullptr;
+      const int64_t max_pos = rot ? M->rot_pos[L.rot_table] : (1ll << 40);
+      STEP(qkv_rotate_cache(f32, M->qkv, qr, a.positions, a.slots, rot, L.rot_dims, (L.mixer_flags & B200_MIXF_ROT_HALF) != 0, max_pos, M->q, W.kc,
+                            W.vc, T, L.heads, L.kv_heads, L.dim, L.vdim, m.block_size, s));
+      const float* sink = (L.mixer_flags & B200_MIXF_SINK) ? W.sink : ((L.mixer_flags & B200_MIXF_SINK_ONE) ? M->zero_sink : nullptr);
+      if (!f32 && paged_attn_mma_supported(L.heads, L.kv_heads, L.dim, L.vdim)) {
+        STEP(step_runs(runs_built));
+        const int seen = L.window > 0 ? std::min(a.max_ctx, L.window + 64) : a.max_ctx;
+        STEP(paged_attn_mma(M->q, (const __nv_bfloat16*)W.kc, (const __nv_bfloat16*)W.vc, a.block_table, a.bt_stride, a.row_to_seq, a.ctx_lens,
+                            (__nv_bfloat16*)M->attn, static_cast<const int32_t*>(M->attn_ws) + 8, static_cast<const int32_t*>(M->attn_ws), T,
+                            L.heads, L.kv_heads, L.dim, L.vdim, m.block_size, L.scale, sink, s,
+                            latent_attn_splits(T, L.heads, L.vdim, seen, M->lat_ws_bytes), M->lat_ws, L.window));
+      } else {
+        if (attn_plan) STEP(step_runs(runs_built));
+        STEP(paged_attn_anydim(f32, M->q, W.kc, W.vc, a.block_table, a.bt_stride, a.row_to_seq, a.ctx_lens, a.positions, nullptr, max_pos,
+                               M->attn, T, L.heads, L.kv_heads, L.dim, L.vdim, m.block_size, L.scale, attn_plan ? 2 : 0, M->attn_ws, s, 0, 0, sink,
+                               L.window));
+      }
+    } else if (is_delta(L)) {
+      const int C = 2 * L.kv_heads * L.dim + av;
+      float* tails = L.conv_taps > 1 ? M->state + W.ctail_off : nullptr;
+      STEP(delta_prep(f32, M->qkv, qr, nullptr, W.conv, W.decay_bias, W.decay_log, a.positions, a.row_to_seq, M->seq_start, seq_slots, tails,
+                      M->slot_floats, M->dq, M->dk, M->dv, M->dbeta, M->ddecay, T, L.heads, L.kv_heads, L.dim, L.vdim, L.conv_taps, 0, 0, s, true));
+      STEP(delta_tails(f32, M->qkv, qr, a.positions, M->seq_start, seq_slots, tails, M->slot_floats, S, C, L.conv_taps, s));
+      STEP(linear_scan(true, M->dq, M->dk, M->dv, M->dbeta, M->ddecay, L.heads, 1, 0, a.positions, M->seq_start, seq_slots, M->state + W.rec_off,
+                       M->slot_floats, M->oraw, S, L.heads, L.kv_heads, L.dim, L.vdim, s));
+      const char* gptr = static_cast<const char*>(M->qkv) + (int64_t)C * es;
+      STEP(head_norm_gate(f32, M->oraw, W.head_norm, gptr, qr, M->attn, T, L.heads, L.vdim, m.norm_eps, s, true));
+    } else {
+      const int gn = L.kv_heads * L.dim, C = av + 2 * gn;
+      float* tails = L.conv_taps > 1 ? M->state + W.ctail_off : nullptr;
+      STEP(ssd_prep(f32, M->qkv, qr, W.conv, W.conv_b, W.decay_bias, W.decay_log, a.positions, a.row_to_seq, M->seq_start, seq_slots, tails,
+                    M->slot_floats, M->dv, M->dk, M->dq, M->dbeta, M->ddecay, T, L.heads, L.kv_heads, L.dim, L.vdim, L.conv_taps, s));
+      const char* xbc = static_cast<const char*>(M->qkv) + (int64_t)av * es;
+      STEP(delta_tails(f32, xbc, qr, a.positions, M->seq_start, seq_slots, tails, M->slot_floats, S, C, L.conv_taps, s));
+      STEP(linear_scan(false, M->dq, M->dk, M->dv, M->dbeta, M->ddecay, L.heads, 1, 0, a.positions, M->seq_start, seq_slots, M->state + W.rec_off,
+                       M->slot_floats, M->oraw, S, L.heads, L.kv_heads, L.dim, L.vdim, s));
+      STEP(ssd_gate_norm(f32, M->oraw, M->dv, W.skip, M->qkv, qr, W.head_norm, M->attn, T, L.heads, L.vdim, L.norm_groups, m.norm_eps, s));
+    }
+    STEP(stack_linear(c, M->attn, av, W.o, M->y, Wd, T, Wd, av, s));
+    y_prev = M->y, parts_prev = nullptr, n_parts_prev = 0, scale_prev = W.scale_mix, hc_prev = W.hc_mix;
+    if (L.mlp == B200_MLP_NONE) continue;
+    STEP(open(W.hc_mlp, W.n_mlp_pre, W.n_mlp_pre_b, W.canon_mlp, W.tail2_off, M->hn, nullptr));
+    if (L.mlp == B200_MLP_DENSE) {
+      if (L.ungated) {
+        STEP(stack_linear(c, M->hn, Wd, W.mlp_gate_up, M->gu, L.ff, T, L.ff, Wd, s));
+        if (L.act == B200_ACT_POLYNORM) STEP(polynorm(f32, M->gu, W.mlp_act, M->ffa, T, L.ff, m.norm_eps, s));
+        else STEP(ff_act(f32, M->gu, M->ffa, T, L.ff, false, L.act, s));
+      } else {
+        STEP(stack_linear(c, M->hn, Wd, W.mlp_gate_up, M->gu, 2 * L.ff, T, 2 * L.ff, Wd, s));
+        STEP(ff_act(f32, M->gu, M->ffa, T, L.ff, true, L.act, s, L.act_limit));
+      }
+      STEP(stack_linear(c, M->ffa, L.ff, W.mlp_down, M->y2, Wd, T, Wd, L.ff, s));
+      y_prev = M->y2, scale_prev = W.scale_mlp, hc_prev = W.hc_mlp;
+    } else {
+      STEP(moe_route(f32, M->hn, W.router, W.router_bias, T, Wd, L.experts, L.top, 1, 1, M->route_ids, M->route_w, s, M->route_logits, c->lin_ws,
+                     c->lin_ws_bytes, L.route_chosen ? 2 : (L.sigmoid_scores ? 1 : 0)));
+      ExpertForm form;
+      form.gated = !L.ungated;
+      form.act = L.act;
+      form.weight_input = L.weight_input != 0;
+      form.limit = L.act_limit;
+      STEP(moe_experts(f32, M->hn, W.e_gate_up, W.e_down, M->route_ids, M->route_w, T, Wd, L.ff, L.experts, L.top, M->parts, M->moe_ws, s, form));
+      y_prev = nullptr, parts_prev = M->parts, n_parts_prev = L.top, scale_prev = W.scale_mlp, hc_prev = W.hc_mlp;
+    }
+  }
+  if (M->tap) {   // the last layer's streams, closed over every row
+    STEP(hyper_step(f32, X, sstride, n, false, y_prev, parts_prev, n_parts_prev, scale_prev, hc_prev, m.residual_mult, nullptr, nullptr, nullptr,
+                    m.norm_eps, nullptr, nullptr, nullptr, M->tap + (int64_t)(nL - 1) * T * Wd, T, Wd, s));
+    y_prev = nullptr, parts_prev = nullptr, hc_prev = nullptr;
+  }
+  // logit rows: the last close, the sum of the streams and the output norm over those rows only
+  STEP(hyper_step(f32, X, sstride, n, false, y_prev, parts_prev, n_parts_prev, scale_prev, hc_prev, m.residual_mult, nullptr, M->final_norm,
+                  M->final_norm_b, m.norm_eps, a.logit_rows, nullptr, M->lm_in, nullptr, a.R, Wd, s));
+  STEP(stack_logits_f32(c, a, 0.f, s));
+#undef STEP
+  return B200_OK;
+}
+
 int stack_enqueue_step(b200_ctx* c, const StepArgs& a, cudaStream_t s) {
   StackModel* M = c->stack;
   const b200_stack_cfg& m = M->cfg;
   if (m.form == B200_FORM_PARALLEL) return stack_enqueue_step_parallel(c, a, s);
   if (m.form == B200_FORM_POSTNORM) return stack_enqueue_step_postnorm(c, a, s);
+  if (m.form == B200_FORM_HYPER) return stack_enqueue_step_hyper(c, a, s);
   const bool f32 = m.f32 != 0;
   const int T = a.T, Wd = m.width, nL = m.n_layers;
   int rc;
@@ -681,6 +871,33 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
       }
       B200_REQUIRE(L.mlp == B200_MLP_NONE || (L.mlp == B200_MLP_DENSE && L.ff > 0 && L.act >= 0 && L.act <= B200_ACT_RELU), B200_ERR_UNSUPPORTED,
                    "stack_create: layer %d: the post-norm form has dense feed-forwards", l);
+    } else if (cfg->form == B200_FORM_HYPER) {
+      B200_REQUIRE(L.heads > 0 && L.dim > 0 && L.vdim > 0 && L.window >= 0 && L.kv_heads > 0 && L.heads % L.kv_heads == 0, B200_ERR_INVALID,
+                   "stack_create: layer %d: bad mixer sizes", l);
+      if (L.mixer == B200_MIXER_ATTENTION) {
+        B200_REQUIRE((L.mixer_flags & B200_MIXF_NO_QK_NORM) && !(L.mixer_flags & (B200_MIXF_HEAD_NORM | B200_MIXF_VALUE_IS_KEY)), B200_ERR_UNSUPPORTED,
+                     "stack_create: layer %d: attention of the multi-stream form has plain q/k/v projections", l);
+        B200_REQUIRE(L.rot_dims >= 0 && L.rot_dims <= L.dim && L.rot_dims % 2 == 0 && L.rot_table < 16, B200_ERR_INVALID,
+                     "stack_create: layer %d: bad attention sizes", l);
+      } else if (L.mixer == B200_MIXER_DELTA) {
+        B200_REQUIRE(head_decay(L), B200_ERR_UNSUPPORTED, "stack_create: layer %d: the delta mixer of the multi-stream form has one decay per head", l);
+        B200_REQUIRE(L.dim <= 256 && L.conv_taps >= 1 && L.conv_taps <= 64 && cfg->n_state_slots > 0, B200_ERR_INVALID,
+                     "stack_create: layer %d: bad recurrent sizes (or no state slots)", l);
+      } else if (L.mixer == B200_MIXER_SSD) {
+        B200_REQUIRE(L.dim <= 256 && L.conv_taps >= 1 && L.conv_taps <= 64 && L.norm_groups >= 1 && (L.heads * L.vdim) % L.norm_groups == 0 &&
+                         cfg->n_state_slots > 0,
+                     B200_ERR_INVALID, "stack_create: layer %d: bad state-space sizes (or no state slots)", l);
+      } else {
+        B200_REQUIRE(false, B200_ERR_UNSUPPORTED, "stack_create: layer %d: mixer %d is not served in the multi-stream form", l, L.mixer);
+      }
+      B200_REQUIRE(L.mlp == B200_MLP_NONE || L.mlp == B200_MLP_MOE || L.mlp == B200_MLP_DENSE, B200_ERR_UNSUPPORTED,
+                   "stack_create: layer %d: unknown feed-forward %d", l, L.mlp);
+      B200_REQUIRE(L.mlp == B200_MLP_NONE || (L.ff > 0 && L.act >= 0 && L.act <= B200_ACT_POLYNORM && !L.shared_ff), B200_ERR_INVALID,
+                   "stack_create: layer %d: bad feed-forward sizes", l);
+      B200_REQUIRE(L.act != B200_ACT_POLYNORM || (L.mlp == B200_MLP_DENSE && L.ungated), B200_ERR_UNSUPPORTED,
+                   "stack_create: layer %d: the polynomial activation belongs to an ungated dense feed-forward", l);
+      B200_REQUIRE(L.act != B200_ACT_SWIGLU_CLAMP || (!L.ungated && L.act_limit > 0.f), B200_ERR_INVALID,
+                   "stack_create: layer %d: the clamped gate needs a gate projection and a positive limit", l);
     } else {
     B200_REQUIRE(L.mixer == B200_MIXER_ATTENTION, B200_ERR_UNSUPPORTED, "stack_create: layer %d: unknown mixer %d", l, L.mixer);
     B200_REQUIRE(L.heads > 0 && L.kv_heads > 0 && L.heads % L.kv_heads == 0 && L.dim > 0 && L.vdim > 0 && L.dim % 2 == 0 &&
@@ -708,19 +925,22 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
     if (is_mlstm(L)) max_gates = std::max(max_gates, 2 * L.heads);
     max_heads = std::max(max_heads, L.heads);
     if (is_latent(L) && L.q_rank > 0) max_qrank = std::max(max_qrank, L.q_rank), max_qh = std::max(max_qh, L.heads * L.dim);
-    if (is_delta(L)) {
-      max_dhd = std::max(max_dhd, L.heads * L.dim);
+    if (is_delta(L) || is_ssd(L)) {
+      max_dhd = std::max(max_dhd, L.heads * (head_decay(L) || is_ssd(L) ? 1 : L.dim));
       max_dqk = std::max(max_dqk, L.kv_heads * L.dim);
       max_dav = std::max(max_dav, L.heads * L.vdim);
       max_dh = std::max(max_dh, L.heads);
     }
-    if (L.mlp == B200_MLP_DENSE) max_gu = std::max(max_gu, 2 * L.ff), max_ffa = std::max(max_ffa, L.ff);
+    if (L.mlp == B200_MLP_DENSE) max_gu = std::max(max_gu, (L.ungated ? 1 : 2) * L.ff), max_ffa = std::max(max_ffa, L.ff);
     if (L.shared_ff > 0) max_gu = std::max(max_gu, 2 * L.shared_ff), max_ffa = std::max(max_ffa, L.shared_ff);
   }
-  const bool par = cfg->form == B200_FORM_PARALLEL, post = cfg->form == B200_FORM_POSTNORM;
-  B200_REQUIRE(par || (!cfg->canon_taps && !cfg->depth_avg && !cfg->bigram_buckets && cfg->logit_softcap == 0.f), B200_ERR_UNSUPPORTED,
-               "stack_create: convolution, depth average, bigram rows and the logit cap belong to the parallel form");
-  B200_REQUIRE(!par || (cfg->canon_taps >= 0 && cfg->canon_taps <= 8 && cfg->n_state_slots >= 0 &&
+  const bool par = cfg->form == B200_FORM_PARALLEL, post = cfg->form == B200_FORM_POSTNORM, hyp = cfg->form == B200_FORM_HYPER;
+  B200_REQUIRE(par || ((hyp || !cfg->canon_taps) && !cfg->depth_avg && !cfg->bigram_buckets && cfg->logit_softcap == 0.f), B200_ERR_UNSUPPORTED,
+               "stack_create: depth average, bigram rows and the logit cap belong to the parallel form, the input convolution to it and the multi-stream form");
+  B200_REQUIRE(!hyp || (cfg->streams >= 1 && cfg->streams <= B200_MAX_STREAMS && cfg->canon_taps >= 0 && cfg->canon_taps <= 16 &&
+                        (cfg->canon_taps <= 1 || cfg->n_state_slots > 0)),
+               B200_ERR_INVALID, "stack_create: bad stream count or convolution taps, or no state slots");
+  B200_REQUIRE(!par || (cfg->canon_taps >= 0 && cfg->canon_taps <= 16 && cfg->n_state_slots >= 0 &&
                         ((cfg->canon_taps <= 1 && cfg->bigram_buckets <= 0) || cfg->n_state_slots > 0)),
                B200_ERR_INVALID, "stack_create: bad convolution taps or no state slots");
   b200_ctx* c = new b200_ctx();
@@ -759,6 +979,30 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
     }
     M->slot_floats = std::max<int64_t>(off, 4);
   }
+  if (hyp && cfg->n_state_slots > 0) {
+    // one slot, per layer: the tails of the two input convolutions [taps - 1][width] (the second only with a feed-forward), then for
+    // a recurrent mixer the tail of its own convolution [conv_taps - 1][channels] and its state [heads][vdim][dim]
+    int64_t off = 0;
+    for (int l = 0; l < cfg->n_layers; ++l) {
+      const b200_stack_layer& L = layers[l];
+      if (cfg->canon_taps > 1) {
+        M->w[l].tail_off = off;
+        off += (int64_t)(cfg->canon_taps - 1) * cfg->width;
+        if (L.mlp != B200_MLP_NONE) {
+          M->w[l].tail2_off = off;
+          off += (int64_t)(cfg->canon_taps - 1) * cfg->width;
+        }
+      }
+      if (is_delta(L) || is_ssd(L)) {
+        M->w[l].ctail_off = off;
+        off = up(off + (is_delta(L) ? delta_tail_floats(L.heads, L.kv_heads, L.dim, L.vdim, L.conv_taps)
+                                    : ssd_tail_floats(L.heads, L.kv_heads, L.dim, L.vdim, L.conv_taps)), 4);
+        M->w[l].rec_off = off;
+        off = up(off + delta_state_floats(L.heads, L.dim, L.vdim), 4);
+      }
+    }
+    M->slot_floats = std::max<int64_t>(off, 4);
+  }
   b200_model_cfg& mc = c->cfg;
   memset(&mc, 0, sizeof(mc));
   mc.hidden = cfg->width;
@@ -793,7 +1037,7 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
       shapes.push_back({(int)Wd, layers[l].heads * layers[l].vdim});
       if (layers[l].mlp == B200_MLP_MOE) shapes.push_back({layers[l].experts, (int)Wd});
       if (layers[l].mlp == B200_MLP_DENSE) {
-        shapes.push_back({2 * layers[l].ff, (int)Wd});
+        shapes.push_back({(layers[l].ungated ? 1 : 2) * layers[l].ff, (int)Wd});
         shapes.push_back({(int)Wd, layers[l].ff});
       }
       if (layers[l].shared_ff > 0) {
@@ -842,7 +1086,7 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
       if (is_latent(layers[l]) && latent_attn_mma_supported(layers[l].heads, layers[l].kv_rank + layers[l].rot_dim, layers[l].kv_rank))
         // splitting only happens below one CTA per SM: at most 148 * 16 pairs, 16 splits
         M->lat_ws_bytes = std::max<int64_t>(M->lat_ws_bytes, std::min<int64_t>(T * layers[l].heads, 148 * 16) * 16 * (layers[l].kv_rank + 2) * 4);
-  if (post && !cfg->f32)
+  if ((post || hyp) && !cfg->f32)
     for (int l = 0; l < cfg->n_layers; ++l)
       if (layers[l].mixer == B200_MIXER_ATTENTION && paged_attn_mma_supported(layers[l].heads, layers[l].kv_heads, layers[l].dim, layers[l].vdim))
         M->lat_ws_bytes = std::max<int64_t>(M->lat_ws_bytes, std::min<int64_t>(T * layers[l].heads, 148 * 16) * 16 * (layers[l].vdim + 2) * 4);
@@ -867,18 +1111,19 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
       {(void**)&M->attn_tc_ws, M->attn_tc_ws_bytes},
       {(void**)&M->attn_wide, tc_heads ? T * tc_heads * kHeadDim * 2 : 16},
       {(void**)&c->logits, R * (int64_t)c->logits_ld * 2},
-      {(void**)&c->logits_f32, (cfg->f32 || par || post) ? R * (int64_t)c->logits_ld * 4 : 16},
+      {(void**)&c->logits_f32, (cfg->f32 || par || post || hyp) ? R * (int64_t)c->logits_ld * 4 : 16},
       {(void**)&M->results, par && cfg->depth_avg ? (int64_t)(cfg->n_layers + 1) * T * Wd * 4 : 16},
-      {(void**)&M->h1f, par && cfg->canon_taps >= 1 ? T * Wd * 4 : 16},
-      {(void**)&M->hc, par ? T * Wd * es : 16},
+      {(void**)&M->h1f, (par || hyp) && cfg->canon_taps >= 1 ? T * Wd * 4 : 16},
+      {(void**)&M->hc, (par || hyp) ? T * Wd * es : 16},
+      {(void**)&M->xs, hyp ? (int64_t)cfg->streams * T * Wd * 4 : 16},
       {(void**)&M->lat, T * std::max(max_lat, 1) * es},
-      {(void**)&M->y2, (par || post) ? T * Wd * es : 16},
+      {(void**)&M->y2, (par || post || hyp) ? T * Wd * es : 16},
       {(void**)&M->y3, par ? T * Wd * es : 16},
       {(void**)&M->gu, T * std::max(max_gu, 1) * es},
       {(void**)&M->ffa, T * std::max(max_ffa, 1) * es},
       {(void**)&M->gates_buf, T * std::max(max_gates, 1) * 4},
       {(void**)&M->oraw, (max_gates || max_dav) ? T * max_a * 4 : 16},
-      {(void**)&M->head_f32, (par || post) ? R * (int64_t)cfg->vocab * 4 : 16},
+      {(void**)&M->head_f32, (par || post || hyp) ? R * (int64_t)cfg->vocab * 4 : 16},
       {(void**)&M->seq_start, (T + 2) * 4},
       {(void**)&M->cq, T * std::max(max_qrank, 1) * es},
       {(void**)&M->qh, T * std::max(max_qh, 1) * es},
@@ -916,7 +1161,7 @@ extern "C" int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_lay
     *it.p = static_cast<char*>(c->pool) + off;
     off += up(std::max<int64_t>(it.bytes, 16), 1024);
   }
-  if (!cfg->f32 && !par && !post) c->logits_f32 = nullptr;
+  if (!cfg->f32 && !par && !post && !hyp) c->logits_f32 = nullptr;
   *out = c;
   return B200_OK;
 }
@@ -929,6 +1174,7 @@ extern "C" int b200_stack_set_weight(b200_ctx* c, int32_t layer, int32_t kind, c
   int64_t er = 0, ec = 1;
   const bool par = M->cfg.form == B200_FORM_PARALLEL;
   const bool post = M->cfg.form == B200_FORM_POSTNORM;
+  const bool hyp = M->cfg.form == B200_FORM_HYPER;
   const bool global = kind == B200_SW_EMBED || kind == B200_SW_FINAL_NORM || kind == B200_SW_HEAD || kind == B200_SW_BIGRAM ||
                       kind == B200_SW_FINAL_NORM_BIAS;
   if (!global) B200_REQUIRE(layer >= 0 && layer < M->cfg.n_layers, B200_ERR_INVALID, "stack_set_weight: layer %d out of range", layer);
@@ -944,8 +1190,14 @@ extern "C" int b200_stack_set_weight(b200_ctx* c, int32_t layer, int32_t kind, c
     case B200_SW_Q_LATENT_NORM: er = L.q_rank; break;
     case B200_SW_UQ: er = (int64_t)L.heads * L.dim; ec = L.q_rank; break;
     case B200_SW_CONV: er = 2 * (int64_t)L.kv_heads * L.dim + (int64_t)L.heads * L.vdim; ec = L.conv_taps; break;
+    case B200_SW_CONV_BIAS: er = 2 * (int64_t)L.kv_heads * L.dim + (int64_t)L.heads * L.vdim; break;
     case B200_SW_DECAY_UP: er = (int64_t)L.heads * L.dim; ec = L.decay_rank; break;
-    case B200_SW_DECAY_BIAS: er = (int64_t)L.heads * L.dim; break;
+    case B200_SW_DECAY_BIAS: er = (head_decay(L) || is_ssd(L)) ? L.heads : (int64_t)L.heads * L.dim; break;
+    case B200_SW_NORM_MIX_PRE_BIAS: case B200_SW_NORM_MLP_PRE_BIAS: case B200_SW_SCALE_MIX: case B200_SW_SCALE_MLP: er = Wd; break;
+    case B200_SW_HC_MIX: case B200_SW_HC_MLP: er = (int64_t)M->cfg.streams * (2 + M->cfg.streams); break;
+    case B200_SW_CANON_MLP: er = Wd; ec = M->cfg.canon_taps; break;
+    case B200_SW_SKIP: er = L.heads; break;
+    case B200_SW_MLP_ACT: er = 4; break;
     case B200_SW_DECAY_LOG: er = L.heads; break;
     case B200_SW_GATE_UP: er = (int64_t)L.heads * L.vdim; ec = L.gate_rank; break;
     case B200_SW_O: er = Wd; ec = (int64_t)L.heads * L.vdim; break;
@@ -962,23 +1214,35 @@ extern "C" int b200_stack_set_weight(b200_ctx* c, int32_t layer, int32_t kind, c
     case B200_SW_GATES: er = 2 * (int64_t)L.heads; ec = Wd; break;
     case B200_SW_GATES_BIAS: er = 2 * (int64_t)L.heads; break;
     case B200_SW_HEAD_NORM: er = (int64_t)L.heads * L.vdim; break;
-    case B200_SW_MLP_GATE_UP: case B200_SW_MLP_GATE_UP_INTERLEAVED: er = 2 * (int64_t)L.ff; ec = Wd; break;
+    case B200_SW_MLP_GATE_UP: er = (int64_t)(L.ungated ? 1 : 2) * L.ff; ec = Wd; break;
+    case B200_SW_MLP_GATE_UP_INTERLEAVED: er = 2 * (int64_t)L.ff; ec = Wd; break;
     case B200_SW_MLP_DOWN: er = Wd; ec = L.ff; break;
     case B200_SW_SHARED_UP: er = (int64_t)(L.ungated ? 1 : 2) * L.shared_ff; ec = Wd; break;
     case B200_SW_SHARED_DOWN: er = Wd; ec = L.shared_ff; break;
     default: B200_REQUIRE(false, B200_ERR_INVALID, "stack_set_weight: unknown kind %d", kind);
   }
-  B200_REQUIRE(kind < B200_SW_BIGRAM || par || post, B200_ERR_INVALID, "stack_set_weight: kind %d belongs to another layer form", kind);
-  B200_REQUIRE(kind < B200_SW_NORM_MIX_POST_BIAS || post || kind == B200_SW_MLP_GATE_UP_INTERLEAVED, B200_ERR_INVALID,
+  B200_REQUIRE(kind < B200_SW_BIGRAM || par || post || hyp, B200_ERR_INVALID, "stack_set_weight: kind %d belongs to another layer form", kind);
+  B200_REQUIRE(kind < B200_SW_NORM_MIX_POST_BIAS || post || hyp || kind == B200_SW_MLP_GATE_UP_INTERLEAVED, B200_ERR_INVALID,
                "stack_set_weight: kind %d belongs to the post-norm form", kind);
+  B200_REQUIRE(kind < B200_SW_NORM_MIX_PRE_BIAS || hyp, B200_ERR_INVALID, "stack_set_weight: kind %d belongs to the multi-stream form", kind);
+  if (kind == B200_SW_CONV_BIAS || kind == B200_SW_SKIP)
+    B200_REQUIRE(is_ssd(L), B200_ERR_INVALID, "stack_set_weight: layer %d has no state-space mixer", layer);
+  if (kind == B200_SW_MLP_ACT)
+    B200_REQUIRE(L.mlp == B200_MLP_DENSE && L.act == B200_ACT_POLYNORM, B200_ERR_INVALID, "stack_set_weight: layer %d has no polynomial activation", layer);
+  if (kind == B200_SW_MLP_GATE_UP_INTERLEAVED) B200_REQUIRE(!L.ungated, B200_ERR_INVALID, "stack_set_weight: layer %d has no gate rows to interleave", layer);
   if (kind == B200_SW_Q_LATENT_NORM || kind == B200_SW_UQ)
     B200_REQUIRE(is_latent(L) && L.q_rank > 0, B200_ERR_INVALID, "stack_set_weight: layer %d has no query latent", layer);
   if (kind >= B200_SW_CONV && kind <= B200_SW_GATE_UP)
-    B200_REQUIRE(is_delta(L), B200_ERR_INVALID, "stack_set_weight: layer %d has no delta recurrence", layer);
-  if (kind == B200_SW_UK_T || kind == B200_SW_UV || kind == B200_SW_SINK)
+    B200_REQUIRE((is_delta(L) && (!head_decay(L) || (kind != B200_SW_DECAY_UP && kind != B200_SW_GATE_UP))) ||
+                     (is_ssd(L) && (kind == B200_SW_CONV || kind == B200_SW_DECAY_BIAS || kind == B200_SW_DECAY_LOG)),
+                 B200_ERR_INVALID, "stack_set_weight: layer %d has no recurrence that takes kind %d", layer, kind);
+  if (kind == B200_SW_UK_T || kind == B200_SW_UV)
     B200_REQUIRE(is_latent(L), B200_ERR_INVALID, "stack_set_weight: layer %d has no latent attention", layer);
+  if (kind == B200_SW_SINK)
+    B200_REQUIRE(is_latent(L) || (L.mixer == B200_MIXER_ATTENTION && (L.mixer_flags & B200_MIXF_SINK)), B200_ERR_INVALID,
+                 "stack_set_weight: layer %d has no sink", layer);
   if (kind == B200_SW_GATES || kind == B200_SW_GATES_BIAS || kind == B200_SW_HEAD_NORM)
-    B200_REQUIRE(is_mlstm(L) || (is_delta(L) && kind == B200_SW_HEAD_NORM), B200_ERR_INVALID, "stack_set_weight: layer %d has no recurrence", layer);
+    B200_REQUIRE(is_mlstm(L) || ((is_delta(L) || is_ssd(L)) && kind == B200_SW_HEAD_NORM), B200_ERR_INVALID, "stack_set_weight: layer %d has no recurrence", layer);
   if (kind == B200_SW_MLP_GATE_UP_INTERLEAVED)
     B200_REQUIRE(!M->cfg.f32 && L.ff % 64 == 0 && Wd % 8 == 0, B200_ERR_UNSUPPORTED,
                  "stack_set_weight: interleaved gate|up rows need the bf16 mode, ff %% 64 == 0 and width %% 8 == 0");
@@ -1031,6 +1295,16 @@ extern "C" int b200_stack_set_weight(b200_ctx* c, int32_t layer, int32_t kind, c
     case B200_SW_DECAY_BIAS: M->w[layer].decay_bias = f; break;
     case B200_SW_DECAY_LOG: M->w[layer].decay_log = f; break;
     case B200_SW_GATE_UP: M->w[layer].gate_up = b; break;
+    case B200_SW_NORM_MIX_PRE_BIAS: M->w[layer].n_mix_pre_b = f; break;
+    case B200_SW_NORM_MLP_PRE_BIAS: M->w[layer].n_mlp_pre_b = f; break;
+    case B200_SW_SCALE_MIX: M->w[layer].scale_mix = f; break;
+    case B200_SW_SCALE_MLP: M->w[layer].scale_mlp = f; break;
+    case B200_SW_HC_MIX: M->w[layer].hc_mix = f; break;
+    case B200_SW_HC_MLP: M->w[layer].hc_mlp = f; break;
+    case B200_SW_CANON_MLP: M->w[layer].canon_mlp = f; break;
+    case B200_SW_CONV_BIAS: M->w[layer].conv_b = f; break;
+    case B200_SW_SKIP: M->w[layer].skip = f; break;
+    case B200_SW_MLP_ACT: M->w[layer].mlp_act = f; break;
   }
   return B200_OK;
 }
@@ -1423,4 +1697,95 @@ extern "C" int b200_paged_attn_mma(const float* q, const void* kc, const void* v
   return paged_attn_mma(q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, block_table, bt_stride, row_to_seq, ctx_lens, (__nv_bfloat16*)out,
                         static_cast<const int32_t*>(workspace) + 8, static_cast<const int32_t*>(workspace), T, heads, kv_heads, dim, vdim,
                         block_size, scale, sink, (cudaStream_t)stream, n_splits, part, window);
+}
+
+// ---- per-kernel entry points of the multi-stream form ------------------------------------------------------------------------
+extern "C" int b200_hyper_step(int32_t f32, float* X, int64_t stream_stride, int32_t n, int32_t init, const void* y, const float* parts,
+                               int32_t n_parts, const float* scale, const float* hc_close, float mult, const float* open_in, const float* norm_w,
+                               const float* norm_b, float eps, const int32_t* rows, float* h_f32, void* h_act, float* sum_out, int32_t R,
+                               int32_t width, void* stream) {
+  B200_REQUIRE(X && width > 0 && R >= 0, B200_ERR_INVALID, "hyper_step: bad argument");
+  return hyper_step(f32 != 0, X, stream_stride, n, init != 0, y, parts, n_parts, scale, hc_close, mult, open_in, norm_w, norm_b, eps, rows, h_f32,
+                    h_act, sum_out, R, width, (cudaStream_t)stream);
+}
+
+extern "C" int b200_qkv_rotate_cache(int32_t f32, const void* qkv, int64_t ld, const int32_t* positions, const int32_t* slots, const float* rot,
+                                     int32_t rot_dims, int32_t half_layout, int64_t max_pos, float* q_out, void* kc, void* vc, int32_t T,
+                                     int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim, int32_t block_size, void* stream) {
+  B200_REQUIRE(qkv && positions && slots && q_out && kc && vc && heads > 0 && kv_heads > 0 && dim > 0 && vdim > 0 && block_size > 0 && max_pos > 0,
+               B200_ERR_INVALID, "qkv_rotate_cache: bad argument");
+  return qkv_rotate_cache(f32 != 0, qkv, ld, positions, slots, rot, rot ? rot_dims : 0, half_layout != 0, max_pos, q_out, kc, vc, T, heads, kv_heads,
+                          dim, vdim, block_size, (cudaStream_t)stream);
+}
+
+extern "C" int b200_polynorm(int32_t f32, const void* z, const float* coef, void* out, int32_t T, int32_t ff, float eps, void* stream) {
+  B200_REQUIRE(z && coef && out && ff > 0, B200_ERR_INVALID, "polynorm: bad argument");
+  return polynorm(f32 != 0, z, coef, out, T, ff, eps, (cudaStream_t)stream);
+}
+
+extern "C" int b200_ff_act_limit(int32_t f32, const void* in, void* out, int32_t T, int32_t ff, int32_t gated, int32_t act, float limit,
+                                 void* stream) {
+  B200_REQUIRE(in && out && ff > 0 && act >= 0 && act <= B200_ACT_SWIGLU_CLAMP, B200_ERR_INVALID, "ff_act_limit: bad argument");
+  return ff_act(f32 != 0, in, out, T, ff, gated != 0, act, (cudaStream_t)stream, limit);
+}
+
+extern "C" int b200_moe_route_chosen(int32_t f32, const void* x, const void* w_router, const float* bias, int32_t T, int32_t width, int32_t experts,
+                                     int32_t top, int32_t* out_ids, float* out_w, void* stream) {
+  B200_REQUIRE(x && w_router && out_ids && out_w && width > 0, B200_ERR_INVALID, "moe_route_chosen: bad argument");
+  return moe_route(f32 != 0, x, (const __nv_bfloat16*)w_router, bias, T, width, experts, top, 1, 1, out_ids, out_w, (cudaStream_t)stream, nullptr,
+                   nullptr, 0, 2);
+}
+
+extern "C" int b200_moe_experts_limit(int32_t f32, const void* x, const void* w_up, const void* w_down, const int32_t* ids, const float* wts,
+                                      int32_t T, int32_t width, int32_t ff, int32_t experts, int32_t top, float* parts, void* ws, int32_t gated,
+                                      int32_t act, float limit, void* stream) {
+  B200_REQUIRE(x && w_up && w_down && ids && wts && parts && width > 0 && ff > 0 && experts > 0 && top > 0, B200_ERR_INVALID,
+               "moe_experts_limit: bad argument");
+  ExpertForm form;
+  form.gated = gated != 0;
+  form.act = act;
+  form.limit = limit;
+  return moe_experts(f32 != 0, x, (const __nv_bfloat16*)w_up, (const __nv_bfloat16*)w_down, ids, wts, T, width, ff, experts, top, parts, ws,
+                     (cudaStream_t)stream, form);
+}
+
+extern "C" int b200_delta_prep_head(int32_t f32, const void* fused, int64_t ld, const float* conv_w, const float* dt_bias, const float* a_log,
+                                    const int32_t* positions, const int32_t* row_to_seq, const int32_t* seq_start, const int32_t* seq_slots,
+                                    const float* tails, int64_t slot_stride, float* qn, float* kn, float* vn, float* beta, float* decay, int32_t T,
+                                    int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim, int32_t taps, void* stream) {
+  B200_REQUIRE(fused && conv_w && dt_bias && a_log && positions && seq_start && qn && kn && vn && beta && decay, B200_ERR_INVALID,
+               "delta_prep_head: null argument");
+  return delta_prep(f32 != 0, fused, ld, nullptr, conv_w, dt_bias, a_log, positions, row_to_seq, seq_start, seq_slots, tails, slot_stride, qn, kn, vn,
+                    beta, decay, T, heads, kv_heads, dim, vdim, taps, 0, 0, (cudaStream_t)stream, true);
+}
+
+extern "C" int b200_linear_scan(int32_t delta_rule, const float* qn, const float* kn, const float* vn, const float* beta, const float* decay,
+                                int64_t g_row, int32_t g_head, int32_t g_chan, const int32_t* positions, const int32_t* seq_start,
+                                const int32_t* seq_slots, float* state, int64_t slot_stride, float* out, int32_t S, int32_t heads, int32_t kv_heads,
+                                int32_t dim, int32_t vdim, void* stream) {
+  B200_REQUIRE(qn && kn && vn && beta && decay && out, B200_ERR_INVALID, "linear_scan: null argument");
+  return linear_scan(delta_rule != 0, qn, kn, vn, beta, decay, g_row, g_head, g_chan, positions, seq_start, seq_slots, state, slot_stride, out, S,
+                     heads, kv_heads, dim, vdim, (cudaStream_t)stream);
+}
+
+extern "C" int b200_head_norm_gate_act(int32_t f32, const float* o, const float* w, const void* gate, int64_t ldg, void* out, int32_t T,
+                                       int32_t heads, int32_t vdim, float eps, int32_t gate_silu, void* stream) {
+  B200_REQUIRE(o && out && heads > 0 && vdim > 0, B200_ERR_INVALID, "head_norm_gate_act: bad argument");
+  return head_norm_gate(f32 != 0, o, w, gate, ldg, out, T, heads, vdim, eps, (cudaStream_t)stream, gate_silu != 0);
+}
+
+extern "C" int b200_ssd_prep(int32_t f32, const void* fused, int64_t ld, const float* conv_w, const float* conv_b, const float* dt_bias,
+                             const float* a_log, const int32_t* positions, const int32_t* row_to_seq, const int32_t* seq_start,
+                             const int32_t* seq_slots, const float* tails, int64_t slot_stride, float* xn, float* bn, float* cn, float* dt,
+                             float* decay, int32_t T, int32_t heads, int32_t groups, int32_t state, int32_t vdim, int32_t taps, void* stream) {
+  B200_REQUIRE(fused && conv_w && dt_bias && a_log && positions && seq_start && xn && bn && cn && dt && decay, B200_ERR_INVALID,
+               "ssd_prep: null argument");
+  return ssd_prep(f32 != 0, fused, ld, conv_w, conv_b, dt_bias, a_log, positions, row_to_seq, seq_start, seq_slots, tails, slot_stride, xn, bn, cn,
+                  dt, decay, T, heads, groups, state, vdim, taps, (cudaStream_t)stream);
+}
+
+extern "C" int b200_ssd_gate_norm(int32_t f32, const float* o, const float* xn, const float* skip, const void* z, int64_t ldz, const float* w,
+                                  void* out, int32_t T, int32_t heads, int32_t vdim, int32_t norm_groups, float eps, void* stream) {
+  B200_REQUIRE(o && xn && skip && z && w && out && heads > 0 && vdim > 0, B200_ERR_INVALID, "ssd_gate_norm: bad argument");
+  return ssd_gate_norm(f32 != 0, o, xn, skip, z, ldz, w, out, T, heads, vdim, norm_groups, eps, (cudaStream_t)stream);
 }

@@ -151,7 +151,7 @@ parallel_close_kernel(float* __restrict__ u, const AT* __restrict__ y_mix, const
 // stays inside the step's portion of the sequence are one CTA each.  The first row of a portion also serves the next
 // taps - 2 rows (those whose window reaches into the state slot's tail), then writes the new tail: every read of the old
 // tail happens in the one CTA that overwrites it.
-constexpr int kMaxTaps = 8;
+constexpr int kMaxTaps = 16;
 template <typename AT>
 __global__ void __launch_bounds__(256)
 canon_conv_kernel(const float* __restrict__ h, const float* __restrict__ w, AT* __restrict__ out, int width, int taps,
@@ -226,13 +226,13 @@ rms_rows_kernel(const float* __restrict__ u, const int32_t* __restrict__ rows, c
 // gated: out[t][f] = act(in[t][f]) * in[t][ff + f] over rows of 2 ff; plain: out[t][f] = act(in[t][f]) (in place allowed)
 template <typename AT>
 __global__ void __launch_bounds__(256)
-ff_act_kernel(const AT* __restrict__ in, AT* __restrict__ out, int64_t total, int ff, int gated, int kind) {
+ff_act_kernel(const AT* __restrict__ in, AT* __restrict__ out, int64_t total, int ff, int gated, int kind, float limit) {
   pdl_wait();
   pdl_launch_dependents();
   for (int64_t i = blockIdx.x * 256ll + threadIdx.x; i < total; i += gridDim.x * 256ll) {
     if (gated) {
       const int64_t t = i / ff, f = i % ff;
-      stx<AT>(out, i, act_apply(ldx<AT>(in, t * 2 * ff + f), kind) * ldx<AT>(in, t * 2 * ff + ff + f));
+      stx<AT>(out, i, gate_combine(ldx<AT>(in, t * 2 * ff + f), ldx<AT>(in, t * 2 * ff + ff + f), kind, limit));
     } else {
       stx<AT>(out, i, act_apply(ldx<AT>(in, i), kind));
     }
@@ -336,15 +336,15 @@ int rms_rows(bool f32, const float* u, const int32_t* rows, const float* g, void
   return B200_OK;
 }
 
-int ff_act(bool f32, const void* in, void* out, int T, int ff, bool gated, int kind, cudaStream_t s) {
+int ff_act(bool f32, const void* in, void* out, int T, int ff, bool gated, int kind, cudaStream_t s, float limit) {
   const int64_t total = (int64_t)T * ff;
   if (total == 0) return B200_OK;
   const int grid = (int)std::min<int64_t>((total + 255) / 256, 148 * 16);
   if (f32)
-    B200_CUDA(launch(ff_act_kernel<float>, dim3(grid), dim3(256), (size_t)0, s, (const float*)in, (float*)out, total, ff, gated ? 1 : 0, kind));
+    B200_CUDA(launch(ff_act_kernel<float>, dim3(grid), dim3(256), (size_t)0, s, (const float*)in, (float*)out, total, ff, gated ? 1 : 0, kind, limit));
   else
     B200_CUDA(launch(ff_act_kernel<__nv_bfloat16>, dim3(grid), dim3(256), (size_t)0, s, (const __nv_bfloat16*)in, (__nv_bfloat16*)out, total,
-                     ff, gated ? 1 : 0, kind));
+                     ff, gated ? 1 : 0, kind, limit));
   return B200_OK;
 }
 

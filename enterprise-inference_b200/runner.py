@@ -437,18 +437,39 @@ class StackRunner(ModelRunner):
                 self._tables.append(spec.table(max(max_model_len, 16)).to(self.device))
             return keys[k]
 
-        from .config import AttentionSpec, ChannelDeltaSpec, DupolornConfig, FutidraConfig, MLSTMSpec
+        from .config import AttentionSpec, ChannelDeltaSpec, DupolornConfig, FutidraConfig, HeadDeltaSpec, MLSTMSpec, RudolixConfig, StateSpaceSpec
         self.parallel = isinstance(cfg, DupolornConfig)
         self.postnorm = isinstance(cfg, FutidraConfig)
+        self.hyper = isinstance(cfg, RudolixConfig)
         # dense feed-forwards of the post-norm form in bf16: gate activation and product in the gate|up linear's epilogue
         self.fuse_gate_up = self.postnorm and not self.f32 and os.environ.get("B200_STACK_FUSE_GATE_UP", "1") != "0"
-        stateful = (self.parallel or self.postnorm) and cfg.needs_state
+        stateful = (self.parallel or self.postnorm or self.hyper) and cfg.needs_state
         self.n_state_slots = int(n_state_slots) if stateful else 0
         if stateful and self.n_state_slots <= 0:
             raise ValueError("this model keeps per-sequence state: n_state_slots must be positive")
         layers = (_abi.StackLayer * cfg.n_layers)()
         for i, L in enumerate(cfg.layers):
             a, f = L.mixer, L.mlp
+            if self.hyper:
+                if isinstance(a, AttentionSpec):
+                    flags = (0 if a.qk_norm else _abi.MIXF_NO_QK_NORM) | (_abi.MIXF_ROT_HALF if a.rot_half else 0) | \
+                            (_abi.MIXF_SINK if a.sink else 0) | (_abi.MIXF_SINK_ONE if a.sink_one else 0)
+                    d = dict(mixer=_abi.MIXER_ATTENTION, heads=a.heads, kv_heads=a.kv_heads, dim=a.dim, vdim=a.vdim,
+                             rot_dims=a.rot.dims if a.rot else 0, rot_table=table_of(a.rot), vrot_table=-1, scale=a.scale,
+                             mixer_flags=flags, window=a.window)
+                elif isinstance(a, HeadDeltaSpec):
+                    d = dict(mixer=_abi.MIXER_DELTA, heads=a.heads, kv_heads=a.kv_heads, dim=a.dim, vdim=a.vdim, rot_table=-1, vrot_table=-1,
+                             conv_taps=a.conv, mixer_flags=_abi.MIXF_HEAD_DECAY)
+                else:
+                    d = dict(mixer=_abi.MIXER_SSD, heads=a.heads, kv_heads=a.groups, dim=a.state, vdim=a.vdim, rot_table=-1, vrot_table=-1,
+                             conv_taps=a.conv, norm_groups=a.norm_groups)
+                if f is not None and f.kind == "dense":
+                    d.update(mlp=_abi.MLP_DENSE, ff=f.ff, act=_abi.ACTS[f.act], ungated=int(not f.gated), act_limit=f.limit)
+                elif f is not None:
+                    d.update(mlp=_abi.MLP_MOE, experts=f.experts, top=f.top, groups=1, keep=1, ff=f.ff, act=_abi.ACTS[f.act],
+                             ungated=int(not f.gated), act_limit=f.limit, route_chosen=int(f.router == "chosen_softmax"))
+                layers[i] = _abi.StackLayer(**d)
+                continue
             if self.postnorm:
                 if isinstance(a, AttentionSpec):
                     flags = (_abi.MIXF_HEAD_NORM if a.head_norm else 0) | (_abi.MIXF_VALUE_IS_KEY if a.value_is_key else 0) | \
@@ -496,6 +517,9 @@ class StackRunner(ModelRunner):
             sc.logit_softcap, sc.n_state_slots = cfg.logit_softcap, self.n_state_slots
         if self.postnorm:
             sc.form, sc.residual_alpha, sc.n_state_slots = _abi.FORM_POSTNORM, cfg.postln_alpha, self.n_state_slots
+        if self.hyper:
+            sc.form, sc.canon_taps, sc.n_state_slots = _abi.FORM_HYPER, cfg.canon_taps, self.n_state_slots
+            sc.streams, sc.residual_mult = cfg.streams, cfg.residual_mult
         h = C.c_void_p()
         _abi.check(self.lib.b200_stack_create(C.byref(sc), layers, C.byref(h)))
         self.ctx = h
@@ -663,6 +687,71 @@ class StackRunner(ModelRunner):
                 self._set(i, A.SW_MLP_GATE_UP, rnd(2 * f.ff, c.width))
                 self._set(i, A.SW_MLP_DOWN, rnd(c.width, f.ff))
 
+    def _init_random_hyper(self, seed: int, std: float):
+        from .config import AttentionSpec, HeadDeltaSpec
+        c, A = self.cfg, _abi
+        g = torch.Generator(device=self.device)
+        g.manual_seed(seed)
+
+        def rnd(*shape, sd=std):
+            t = torch.empty(shape, dtype=torch.bfloat16, device=self.device)
+            t.normal_(0.0, sd, generator=g)
+            return t
+
+        ones, zeros = torch.ones(c.width, device=self.device), torch.zeros(c.width, device=self.device)
+        n = c.streams
+        # every stream is read and written with equal weight; the streams keep themselves
+        hc = torch.cat([torch.full((n,), 1.0 / n), torch.ones(n), torch.eye(n).reshape(-1)]).to(self.device)
+        emb = rnd(c.vocab, c.width, sd=1.0)
+        self._set(0, A.SW_EMBED, emb)
+        self._set(0, A.SW_HEAD, emb)
+        self._set(0, A.SW_FINAL_NORM, ones)
+        self._set(0, A.SW_FINAL_NORM_BIAS, zeros)
+        for i, L in enumerate(c.layers):
+            a, f = L.mixer, L.mlp
+            self._set(i, A.SW_NORM_MIX_PRE, ones)
+            self._set(i, A.SW_NORM_MIX_PRE_BIAS, zeros)
+            self._set(i, A.SW_SCALE_MIX, ones)
+            self._set(i, A.SW_HC_MIX, hc)
+            if c.canon_taps >= 1:
+                self._set(i, A.SW_CANON, rnd(c.width, c.canon_taps, sd=0.2).float())
+            self._set(i, A.SW_QKV, rnd(c.mixer_rows(a), c.width))
+            if isinstance(a, AttentionSpec):
+                if a.sink:
+                    self._set(i, A.SW_SINK, torch.zeros(a.heads, device=self.device))
+            elif isinstance(a, HeadDeltaSpec):
+                self._set(i, A.SW_CONV, rnd(2 * a.kv_heads * a.dim + a.heads * a.vdim, a.conv, sd=0.5).float())
+                self._set(i, A.SW_DECAY_BIAS, torch.zeros(a.heads, device=self.device))
+                self._set(i, A.SW_DECAY_LOG, torch.zeros(a.heads, device=self.device))
+                self._set(i, A.SW_HEAD_NORM, torch.ones(a.heads * a.vdim, device=self.device))
+            else:
+                ch = a.heads * a.vdim + 2 * a.groups * a.state
+                self._set(i, A.SW_CONV, rnd(ch, a.conv, sd=0.5).float())
+                self._set(i, A.SW_CONV_BIAS, torch.zeros(ch, device=self.device))
+                self._set(i, A.SW_DECAY_BIAS, torch.zeros(a.heads, device=self.device))
+                self._set(i, A.SW_DECAY_LOG, torch.zeros(a.heads, device=self.device))
+                self._set(i, A.SW_SKIP, torch.ones(a.heads, device=self.device))
+                self._set(i, A.SW_HEAD_NORM, torch.ones(a.heads * a.vdim, device=self.device))
+            self._set(i, A.SW_O, rnd(c.width, a.heads * a.vdim))
+            if f is None:
+                continue
+            self._set(i, A.SW_NORM_MLP_PRE, ones)
+            self._set(i, A.SW_NORM_MLP_PRE_BIAS, zeros)
+            self._set(i, A.SW_SCALE_MLP, ones)
+            self._set(i, A.SW_HC_MLP, hc)
+            if c.canon_taps >= 1:
+                self._set(i, A.SW_CANON_MLP, rnd(c.width, c.canon_taps, sd=0.2).float())
+            if f.kind == "dense":
+                self._set(i, A.SW_MLP_GATE_UP, rnd((2 if f.gated else 1) * f.ff, c.width))
+                self._set(i, A.SW_MLP_DOWN, rnd(c.width, f.ff))
+                if f.act == "polynorm":
+                    self._set(i, A.SW_MLP_ACT, torch.tensor([1.0, 0.5, 0.25, 0.0], device=self.device))
+            else:
+                self._set(i, A.SW_ROUTER, rnd(f.experts, c.width))
+                self._set(i, A.SW_ROUTER_BIAS, torch.zeros(f.experts, device=self.device))
+                self._set(i, A.SW_EXPERT_GATE_UP, rnd(f.experts * (2 if f.gated else 1) * f.ff, c.width))
+                self._set(i, A.SW_EXPERT_DOWN, rnd(f.experts * c.width, f.ff))
+
     def set_step_slots(self, seq_slots: Optional[torch.Tensor]):
         """Device-pointer steps (step_device) of a model with state slots: int32 device tensor, one slot per sequence of the step."""
         self._step_slots = seq_slots
@@ -674,6 +763,8 @@ class StackRunner(ModelRunner):
             return self._init_random_parallel(seed, std)
         if self.postnorm:
             return self._init_random_postnorm(seed, std)
+        if self.hyper:
+            return self._init_random_hyper(seed, std)
         c, A = self.cfg, _abi
         g = torch.Generator(device=self.device)
         g.manual_seed(seed)

@@ -230,4 +230,67 @@ def futidra_weights(w: Dict[str, torch.Tensor], cfg) -> Iterator[Tuple[int, int,
             yield i, A.SW_MLP_DOWN, w[p + "mlp.down"]
 
 
-STACK_WEIGHT_MAPS = {"Bopilorn": bopilorn_weights, "Dupolorn": dupolorn_weights, "Futidra": futidra_weights}
+def rudolix_weights(w: Dict[str, torch.Tensor], cfg) -> Iterator[Tuple[int, int, torch.Tensor]]:
+    """(layer, b200_stack_weight kind, tensor) of a Rudolix checkpoint: `embed` (also the output projection), `final.norm[.b]`, per
+    layer i the pre-norms `l<i>.norm1[.b]`, `l<i>.norm2[.b]`, the per-channel result scales `l<i>.ls1|ls2`, the stream coefficients
+    `l<i>.hc1|hc2.in|out|mix` (packed in | out | mix), the input convolutions `l<i>.canon1|canon2`, the mixer `l<i>.mix.*` and the
+    feed-forward `l<i>.mlp.*`.  Projections of the mixer's input are fused row-wise: attention q | k | v; delta q | k | v | g | b | a;
+    the state-space mixer's `in` is one tensor already (z | x | B | C | dt).  The delta mixer's read-out weight is repeated for every
+    head, its three convolution kernels are stacked; an expert's gate and up rows are stacked per expert; vectors go over in fp32."""
+    from . import _abi as A
+    from .config import AttentionSpec, HeadDeltaSpec
+    yield 0, A.SW_EMBED, w["embed"]
+    yield 0, A.SW_HEAD, w["embed"]
+    yield 0, A.SW_FINAL_NORM, w["final.norm"]
+    yield 0, A.SW_FINAL_NORM_BIAS, w["final.norm.b"]
+    taps = cfg.canon_taps
+
+    def hc(prefix):
+        return torch.cat([w[prefix + ".in"].reshape(-1).float(), w[prefix + ".out"].reshape(-1).float(), w[prefix + ".mix"].reshape(-1).float()])
+
+    for i, L in enumerate(cfg.layers):
+        p, a, f = f"l{i}.", L.mixer, L.mlp
+        yield i, A.SW_NORM_MIX_PRE, w[p + "norm1"]
+        yield i, A.SW_NORM_MIX_PRE_BIAS, w[p + "norm1.b"]
+        yield i, A.SW_SCALE_MIX, w[p + "ls1"]
+        yield i, A.SW_HC_MIX, hc(p + "hc1")
+        if taps >= 1:
+            yield i, A.SW_CANON, w[p + "canon1"]
+        if isinstance(a, AttentionSpec):
+            yield i, A.SW_QKV, torch.cat([w[p + "mix.q"], w[p + "mix.k"], w[p + "mix.v"]], 0)
+            yield i, A.SW_SINK, w[p + "mix.sink"]
+        elif isinstance(a, HeadDeltaSpec):
+            yield i, A.SW_QKV, torch.cat([w[p + "mix." + n] for n in ("q", "k", "v", "g", "b", "a")], 0)
+            yield i, A.SW_CONV, torch.cat([w[p + "mix.q.conv"], w[p + "mix.k.conv"], w[p + "mix.v.conv"]], 0)
+            yield i, A.SW_DECAY_BIAS, w[p + "mix.dt_bias"]
+            yield i, A.SW_DECAY_LOG, w[p + "mix.A_log"]
+            yield i, A.SW_HEAD_NORM, w[p + "mix.norm"].repeat(a.heads)
+        else:
+            yield i, A.SW_QKV, w[p + "mix.in"]
+            yield i, A.SW_CONV, w[p + "mix.conv"]
+            yield i, A.SW_CONV_BIAS, w[p + "mix.conv.b"]
+            yield i, A.SW_DECAY_BIAS, w[p + "mix.dt_bias"]
+            yield i, A.SW_DECAY_LOG, w[p + "mix.A_log"]
+            yield i, A.SW_SKIP, w[p + "mix.D"]
+            yield i, A.SW_HEAD_NORM, w[p + "mix.norm"]
+        yield i, A.SW_O, w[p + "mix.o"]
+        if f is None:
+            continue
+        yield i, A.SW_NORM_MLP_PRE, w[p + "norm2"]
+        yield i, A.SW_NORM_MLP_PRE_BIAS, w[p + "norm2.b"]
+        yield i, A.SW_SCALE_MLP, w[p + "ls2"]
+        yield i, A.SW_HC_MLP, hc(p + "hc2")
+        if taps >= 1:
+            yield i, A.SW_CANON_MLP, w[p + "canon2"]
+        if f.kind == "dense":
+            yield i, A.SW_MLP_GATE_UP, w[p + "mlp.up"]
+            yield i, A.SW_MLP_DOWN, w[p + "mlp.down"]
+            yield i, A.SW_MLP_ACT, w[p + "mlp.act"]
+        else:
+            yield i, A.SW_ROUTER, w[p + "mlp.router"]
+            yield i, A.SW_ROUTER_BIAS, w[p + "mlp.router.b"]
+            yield i, A.SW_EXPERT_GATE_UP, torch.cat([t for e in range(f.experts) for t in (w[f"{p}mlp.e{e}.gate"], w[f"{p}mlp.e{e}.up"])], 0)
+            yield i, A.SW_EXPERT_DOWN, torch.cat([w[f"{p}mlp.e{e}.down"] for e in range(f.experts)], 0)
+
+
+STACK_WEIGHT_MAPS = {"Bopilorn": bopilorn_weights, "Dupolorn": dupolorn_weights, "Futidra": futidra_weights, "Rudolix": rudolix_weights}

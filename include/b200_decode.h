@@ -407,13 +407,38 @@ B200_API int b200_tp_allreduce(b200_ctx* ctx, int32_t buf_idx, const void* parti
  * dim^-1/2); beta = sigmoid(w_b . h) per head; decay = exp(-exp(a_log[head]) softplus(W_a2 (W_a1 h) + dt_bias)) per head and
  * key channel; per head  S = diag(decay) S;  u = beta (v - S^T k);  S += k u^T;  o = S^T q;  o is brought to unit RMS per
  * head, times a weight, times sigmoid(W_g2 (W_g1 h)).  S (fp32) and the last conv_taps - 1 inputs of the convolution live
- * in the sequence's state slot. */
-typedef enum b200_mixer_kind { B200_MIXER_ATTENTION = 1, B200_MIXER_LATENT = 2, B200_MIXER_MLSTM = 3, B200_MIXER_DELTA = 4 } b200_mixer_kind;
+ * in the sequence's state slot.
+ *
+ * Fourth layer form (b200_stack_cfg.form = B200_FORM_HYPER): pre-norm sublayers over `streams` fp32 copies X_1..X_n of the
+ * residual, all equal to the scaled embedding at the start.  Sublayer q of a layer has coefficients a_q [n], b_q [n], M_q [n][n]:
+ *   u = sum_s a_q[s] X_s;   h = LN(u) * w + bias;   h += conv(h)   (causal per-channel convolution over canon_taps steps, its
+ *   last canon_taps - 1 inputs in the state slot, for BOTH sublayers);   y = scale_q * sublayer(h)   (scale_q [width]);
+ *   X_t = sum_s M_q[s][t] X_s + residual_mult * b_q[t] * y   for every t at once.
+ * The output is LN_final(sum_s X_s) times the head.  Mixers of this form: B200_MIXER_ATTENTION with B200_MIXF_NO_QK_NORM (plain
+ * q/k/v projections), B200_MIXF_ROT_HALF (dimension i of the rotated part turns with dimension i + rot_dims / 2) and
+ * B200_MIXF_SINK (exp(sink[head]) in the softmax denominator);  B200_MIXER_DELTA with B200_MIXF_HEAD_DECAY: one decay per head,
+ * g = exp(-exp(a_log[head]) softplus(w_a . h + dt_bias[head])), single-step projections, fused rows q | k | v | gate | b | a,
+ * read-out times a weight shared by the heads ([vdim] repeated) and silu(gate);  and
+ *
+ * B200_MIXER_SSD: state-space recurrence with a scalar decay per head.  The fused projection is z | x | B | C | dt
+ * (heads*vdim, heads*vdim, kv_heads*dim, kv_heads*dim, heads; kv_heads = groups of heads that share B and C, dim = state size);
+ * x | B | C pass a causal per-channel convolution of conv_taps taps with bias and silu; dt = softplus(dt + dt_bias);
+ * per head  S = exp(-exp(a_log) dt) S + dt B x^T  (S [dim][vdim], fp32, in the state slot);  y = S^T C + D x;  y *= silu(z);
+ * y is brought to unit RMS in `norm_groups` equal parts and multiplied by a weight.
+ *
+ * Feed-forwards of this form: B200_MLP_DENSE with `ungated` and B200_ACT_POLYNORM: down(p(up h)), p(z) = c0 N(z) + c1 N(z^2) +
+ * c2 N(z^3) + c3 with N(v) = v / sqrt(mean(v^2) + eps) over the ff entries of a token;  B200_MLP_MOE with route_chosen: the
+ * router bias joins the logits, the `top` largest logits are chosen and the mixing weights are the softmax over the chosen logits
+ * alone; experts with B200_ACT_SWIGLU_CLAMP: g = min(gate h, act_limit), u = clamp(up h, -act_limit, act_limit),
+ * down(g * sigmoid(1.702 g) * (u + 1)). */
+typedef enum b200_mixer_kind { B200_MIXER_ATTENTION = 1, B200_MIXER_LATENT = 2, B200_MIXER_MLSTM = 3, B200_MIXER_DELTA = 4, B200_MIXER_SSD = 5 } b200_mixer_kind;
 typedef enum b200_mlp_kind { B200_MLP_NONE = 0, B200_MLP_MOE = 1, B200_MLP_DENSE = 2 } b200_mlp_kind;
-typedef enum b200_act_kind { B200_ACT_SILU = 0, B200_ACT_GELU_TANH = 1, B200_ACT_RELU2 = 2, B200_ACT_RELU = 3 } b200_act_kind;
-typedef enum b200_stack_form { B200_FORM_SANDWICH = 0, B200_FORM_PARALLEL = 1, B200_FORM_POSTNORM = 2 } b200_stack_form;
+typedef enum b200_act_kind { B200_ACT_SILU = 0, B200_ACT_GELU_TANH = 1, B200_ACT_RELU2 = 2, B200_ACT_RELU = 3, B200_ACT_SWIGLU_CLAMP = 4,
+                             B200_ACT_POLYNORM = 5 } b200_act_kind;
+typedef enum b200_stack_form { B200_FORM_SANDWICH = 0, B200_FORM_PARALLEL = 1, B200_FORM_POSTNORM = 2, B200_FORM_HYPER = 3 } b200_stack_form;
 enum { B200_MIXF_SINK = 1, B200_MIXF_GATE = 2, B200_MIXF_HEAD_NORM = 4, B200_MIXF_VALUE_IS_KEY = 8, B200_MIXF_SINK_ONE = 16,
-       B200_MIXF_HEAD_GATE = 32 };
+       B200_MIXF_HEAD_GATE = 32, B200_MIXF_ROT_HALF = 64, B200_MIXF_NO_QK_NORM = 128, B200_MIXF_HEAD_DECAY = 256 };
+enum { B200_MAX_STREAMS = 8 };
 
 typedef struct b200_stack_layer {
   int32_t mixer;                       /* b200_mixer_kind */
@@ -438,6 +463,9 @@ typedef struct b200_stack_layer {
   int32_t kv_share;                    /* latent mixer: 1 + the layer whose cached latent rows this layer reads (0: its own) */
   int32_t conv_taps;                   /* delta mixer: taps of the q/k/v convolution (>= 1) */
   int32_t decay_rank, gate_rank;       /* delta mixer: inner sizes of the two-step decay and output-gate projections */
+  int32_t norm_groups;                 /* state-space mixer: equal parts of the gated output that are normalised on their own (>= 1) */
+  float act_limit;                     /* B200_ACT_SWIGLU_CLAMP: the clamp */
+  int32_t route_chosen;                /* router: bias inside the logits, mixing weights = softmax over the chosen logits */
 } b200_stack_layer;
 
 typedef struct b200_stack_cfg {
@@ -455,6 +483,8 @@ typedef struct b200_stack_cfg {
   float logit_softcap;                 /* > 0: logits = cap * tanh(logits / cap) */
   int32_t n_state_slots;               /* per-sequence state slots (previous token, convolution tails, recurrent state) */
   float residual_alpha;                /* post-norm form: the stream's factor inside the norm */
+  int32_t streams;                     /* multi-stream form: copies of the residual (1 .. B200_MAX_STREAMS) */
+  float residual_mult;                 /* multi-stream form: factor of every sublayer's result */
 } b200_stack_cfg;
 
 typedef enum b200_stack_weight {
@@ -503,9 +533,24 @@ typedef enum b200_stack_weight {
   B200_SW_DECAY_BIAS = 35,         /* f32  [heads*dim] */
   B200_SW_DECAY_LOG = 36,          /* f32  [heads] */
   B200_SW_GATE_UP = 37,            /* bf16 [heads*vdim][gate_rank] */
-  B200_SW_MLP_GATE_UP_INTERLEAVED = 38 /* bf16 [2*ff][width] in 128-row slabs: 64 gate rows, then the 64 matching up rows; this OR
+  B200_SW_MLP_GATE_UP_INTERLEAVED = 38, /* bf16 [2*ff][width] in 128-row slabs: 64 gate rows, then the 64 matching up rows; this OR
                                           B200_SW_MLP_GATE_UP.  bf16 mode, ff % 64 == 0, width % 8 == 0: the gate activation and the
                                           product run in the linear's epilogue */
+  /* multi-stream form: NORM_MIX_PRE / NORM_MLP_PRE / FINAL_NORM are the weights [width] of the pre-norms and of the output norm,
+     their biases follow (FINAL_NORM_BIAS above); CANON is the mixer's input convolution.  QKV: attention q | k | v rows; delta
+     q | k | v | gate | b | a rows; state-space z | x | B | C | dt rows.  CONV of a state-space mixer: [heads*vdim + 2*kv_heads*dim]
+     [conv_taps]; DECAY_BIAS of a head-decay delta or state-space mixer: [heads]; HEAD_NORM of a state-space mixer: [heads*vdim].
+     MLP_GATE_UP of an ungated dense feed-forward: [ff][width]. */
+  B200_SW_NORM_MIX_PRE_BIAS = 39,  /* f32 [width] */
+  B200_SW_NORM_MLP_PRE_BIAS = 40,  /* f32 [width] */
+  B200_SW_SCALE_MIX = 41,          /* f32 [width]: per-channel factor of the mixer's result */
+  B200_SW_SCALE_MLP = 42,          /* f32 [width] */
+  B200_SW_HC_MIX = 43,             /* f32 [2 n + n n]: a [n] | b [n] | M [n][n] (from, to) of the mixer sublayer, n = streams */
+  B200_SW_HC_MLP = 44,             /* f32 [2 n + n n] */
+  B200_SW_CANON_MLP = 45,          /* f32 [width][canon_taps]: input convolution of the feed-forward */
+  B200_SW_CONV_BIAS = 46,          /* f32 [conv channels] */
+  B200_SW_SKIP = 47,               /* f32 [heads]: D of a state-space mixer */
+  B200_SW_MLP_ACT = 48             /* f32 [4]: c0..c3 of B200_ACT_POLYNORM */
 } b200_stack_weight;
 
 B200_API int b200_stack_create(const b200_stack_cfg* cfg, const b200_stack_layer* layers, b200_ctx** out);
@@ -709,6 +754,61 @@ B200_API int b200_delta_scan(const float* qn, const float* kn, const float* vn, 
                              const int32_t* positions, const int32_t* seq_start, const int32_t* seq_slots, float* state,
                              int64_t slot_stride, float* out, int32_t n_seqs, int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim,
                              void* stream);
+/* ---- per-kernel entry points of the multi-stream form (unit tests, profiling); f32 as above ---- */
+/* Streams X [n][stream_stride] fp32 (row t of stream s at X + s * stream_stride + t * width).  init: every stream takes the row of
+ * stream 0 first.  With hc_close (a | b | M of the sublayer that ends) X_t = sum_s M[s][t] X_s + mult * b[t] * scale * y, y an
+ * activation row or the sum of n_parts fp32 partial rows.  Then u = sum_s open_in[s] X_s (open_in NULL: ones); with norm_w,
+ * h = LN(u) * norm_w + norm_b into h_f32 and / or h_act, else u itself; sum_out receives sum_s X_s.  rows: only those rows are
+ * read (outputs are dense, the streams are not written). */
+B200_API int b200_hyper_step(int32_t f32, float* X, int64_t stream_stride, int32_t n, int32_t init, const void* y, const float* parts,
+                             int32_t n_parts, const float* scale, const float* hc_close, float mult, const float* open_in,
+                             const float* norm_w, const float* norm_b, float eps, const int32_t* rows, float* h_f32, void* h_act,
+                             float* sum_out, int32_t n_rows, int32_t width, void* stream);
+/* Fused rows [heads*dim q | kv_heads*dim k | kv_heads*vdim v] of leading dimension ld: the leading rot_dims dimensions of every q
+ * and k head turn by table rot [max_pos][2][rot_dims/2], dimension i with i + rot_dims/2 (half_layout) or 2i with 2i + 1; q_out
+ * fp32 [T][heads*dim]; k and v rows into the caches [block][kv_heads][block_size][dim | vdim] at slot_mapping[t]. */
+B200_API int b200_qkv_rotate_cache(int32_t f32, const void* qkv, int64_t ld, const int32_t* positions, const int32_t* slot_mapping,
+                                   const float* rot, int32_t rot_dims, int32_t half_layout, int64_t max_pos, float* q_out, void* k_cache,
+                                   void* v_cache, int32_t n_tokens, int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim,
+                                   int32_t block_size, void* stream);
+/* out[t] = c0 N(z) + c1 N(z^2) + c2 N(z^3) + c3 over rows z [T][ff], N(v) = v / sqrt(mean(v^2) + eps). */
+B200_API int b200_polynorm(int32_t f32, const void* z, const float* coef, void* out, int32_t n_tokens, int32_t ff, float eps, void* stream);
+/* b200_ff_act with the clamp of B200_ACT_SWIGLU_CLAMP. */
+B200_API int b200_ff_act_limit(int32_t f32, const void* in, void* out, int32_t n_tokens, int32_t ff, int32_t gated, int32_t act, float limit,
+                               void* stream);
+/* Router whose bias joins the logits; the `top` largest are chosen, weights = softmax over the chosen logits. */
+B200_API int b200_moe_route_chosen(int32_t f32, const void* x, const void* w_router, const float* bias, int32_t n_tokens, int32_t width,
+                                   int32_t experts, int32_t top, int32_t* out_ids, float* out_w, void* stream);
+/* b200_moe_experts_form with the clamp of B200_ACT_SWIGLU_CLAMP. */
+B200_API int b200_moe_experts_limit(int32_t f32, const void* x, const void* w_up, const void* w_down, const int32_t* ids, const float* wts,
+                                    int32_t n_tokens, int32_t width, int32_t ff, int32_t experts, int32_t top, float* parts, void* ws,
+                                    int32_t gated, int32_t act, float limit, void* stream);
+/* Delta mixer with one decay per head: fused rows q | k | v | gate | b | a (no padding); outputs as b200_delta_prep, decay [T][heads]. */
+B200_API int b200_delta_prep_head(int32_t f32, const void* fused, int64_t ld, const float* conv_w, const float* dt_bias, const float* a_log,
+                                  const int32_t* positions, const int32_t* row_to_seq, const int32_t* seq_start, const int32_t* seq_slots,
+                                  const float* tails, int64_t slot_stride, float* qn, float* kn, float* vn, float* beta, float* decay,
+                                  int32_t n_tokens, int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim, int32_t taps, void* stream);
+/* The recurrence S = g S; u = beta (v - S^T k) (delta_rule) or u = beta v (plain); S += k u^T; o = S^T q, with the decay of
+ * (row t, head h, key channel d) at decay[t * g_row + h * g_head + d * g_chan]. */
+B200_API int b200_linear_scan(int32_t delta_rule, const float* qn, const float* kn, const float* vn, const float* beta, const float* decay,
+                              int64_t g_row, int32_t g_head, int32_t g_chan, const int32_t* positions, const int32_t* seq_start,
+                              const int32_t* seq_slots, float* state, int64_t slot_stride, float* out, int32_t n_seqs, int32_t heads,
+                              int32_t kv_heads, int32_t dim, int32_t vdim, void* stream);
+/* b200_head_norm_gate whose gate is silu(gate) (gate_silu) instead of sigmoid(gate). */
+B200_API int b200_head_norm_gate_act(int32_t f32, const float* o, const float* w, const void* gate, int64_t ldg, void* out, int32_t n_tokens,
+                                     int32_t heads, int32_t vdim, float eps, int32_t gate_silu, void* stream);
+/* State-space mixer, after the projection.  fused [T][ld] = z | x | B | C | dt.  prep: convolution with bias (tails
+ * [slot][taps-1][heads*vdim + 2*groups*state] fp32) + silu -> fp32 xn [T][heads*vdim], bn, cn [T][groups*state]; dt = softplus(dt +
+ * dt_bias) and decay = exp(-exp(a_log) dt) [T][heads].  The tails are written by b200_delta_tails over the x | B | C columns, the
+ * recurrence is b200_linear_scan (plain) with q = cn, k = bn, v = xn, beta = dt.  gate_norm: y = (o + skip[head] xn) * silu(z), unit
+ * RMS in norm_groups equal parts, times w. */
+B200_API int b200_ssd_prep(int32_t f32, const void* fused, int64_t ld, const float* conv_w, const float* conv_b, const float* dt_bias,
+                           const float* a_log, const int32_t* positions, const int32_t* row_to_seq, const int32_t* seq_start,
+                           const int32_t* seq_slots, const float* tails, int64_t slot_stride, float* xn, float* bn, float* cn, float* dt,
+                           float* decay, int32_t n_tokens, int32_t heads, int32_t groups, int32_t state, int32_t vdim, int32_t taps,
+                           void* stream);
+B200_API int b200_ssd_gate_norm(int32_t f32, const float* o, const float* xn, const float* skip, const void* z, int64_t ldz, const float* w,
+                                void* out, int32_t n_tokens, int32_t heads, int32_t vdim, int32_t norm_groups, float eps, void* stream);
 /* y[T][n_out] = x[T][k] . w[n_out][k]^T on CUDA cores in true fp32; w bf16, x / y fp32 or bf16. */
 B200_API int b200_linear_simt(int32_t x_f32, int32_t y_f32, const void* x, int64_t ldx, const void* w, void* y, int64_t ldy,
                      int32_t n_tokens, int32_t n_out, int32_t k, void* stream);
