@@ -687,6 +687,45 @@ def _dupolorn_dense_config(Cf, name, z):
                              logit_softcap=0.0, layers=layers)
 
 
+# Rudolix beside Futidra (the closest model of the framework: grouped-query attention with a value cache on the same tensor-core
+# kernel, the delta rule on the same scan with per-sequence state slots, dense feed-forwards on the same linears) at equal width,
+# layers, heads, head sizes and recurrence heads.  Rudolix's layers cycle the head-decay delta rule (dense feed-forward), attention
+# (routed experts), the state-space mixer (dense) and attention (routed experts) over `streams` residual streams with input
+# convolutions; Futidra's cycle its delta rule and its attention, all with dense feed-forwards of top x expert width, so that a
+# token does the same feed-forward products in both.
+RUDOLIX_SIZES = {
+    "w2048": dict(width=2048, heads=16, kv=4, dim=128, vdim=128, r_heads=16, r_dim=128, r_vdim=128, s_heads=64, s_vdim=64, s_state=128,
+                  conv=4, rank=128, ff=4096, experts=32, top=4, eff=1024, streams=4, taps=4, layers=4, vocab=32768),
+    "w1024": dict(width=1024, heads=16, kv=4, dim=64, vdim=64, r_heads=8, r_dim=128, r_vdim=128, s_heads=32, s_vdim=64, s_state=64,
+                  conv=4, rank=64, ff=2048, experts=16, top=2, eff=1024, streams=4, taps=4, layers=4, vocab=32768),
+}
+
+
+def _rudolix_config(Cf, name, z):
+    rot = Cf.RotarySpec(base=1000000.0, dims=z["dim"] // 2)
+    att = Cf.AttentionSpec(heads=z["heads"], kv_heads=z["kv"], dim=z["dim"], vdim=z["vdim"], scale=z["dim"] ** -0.5, rot=rot, qk_norm=False,
+                           rot_half=True, sink=True)
+    dense = Cf.FeedForwardSpec(kind="dense", ff=z["ff"], act="polynorm", gated=False)
+    moe = Cf.FeedForwardSpec(kind="moe", ff=z["eff"], act="swiglu_clamp", experts=z["experts"], top=z["top"], gated=True, limit=7.0,
+                             router="chosen_softmax")
+    mixers = [(Cf.HeadDeltaSpec(heads=z["r_heads"], kv_heads=z["r_heads"], dim=z["r_dim"], vdim=z["r_vdim"], conv=z["conv"]), dense), (att, moe),
+              (Cf.StateSpaceSpec(heads=z["s_heads"], vdim=z["s_vdim"], state=z["s_state"], groups=1, norm_groups=1, conv=z["conv"]), dense), (att, moe)]
+    layers = [Cf.StackLayerSpec(mixer=mixers[i % 4][0], mlp=mixers[i % 4][1]) for i in range(z["layers"])]
+    return Cf.RudolixConfig(name=name, width=z["width"], vocab=z["vocab"], embed_scale=1.0, canon_taps=z["taps"], streams=z["streams"],
+                            residual_mult=0.5, layers=layers)
+
+
+def _futidra_like_rudolix(Cf, name, z):
+    rot = Cf.RotarySpec(base=1000000.0, dims=z["dim"] // 2)
+    ff = Cf.FeedForwardSpec(kind="dense", ff=z["ff"], act="relu")
+    mixers = [Cf.ChannelDeltaSpec(heads=z["r_heads"], kv_heads=z["r_heads"], dim=z["r_dim"], vdim=z["r_vdim"], conv=z["conv"], decay_rank=z["rank"],
+                                  gate_rank=z["rank"]),
+              Cf.AttentionSpec(heads=z["heads"], kv_heads=z["kv"], dim=z["dim"], vdim=z["dim"], scale=z["dim"] ** -0.5, rot=rot, head_norm=True,
+                               value_is_key=True, sink_one=True)]
+    layers = [Cf.StackLayerSpec(mixer=mixers[i % 2], mlp=ff) for i in range(z["layers"])]
+    return Cf.FutidraConfig(name=name, width=z["width"], vocab=z["vocab"], postln_alpha=2.0, layers=layers)
+
+
 def _design_batch(R, n_seqs, ctx, n_new, bs, vocab):
     """n_seqs sequences that already hold ctx tokens and bring n_new rows each; the last row of each is a logit row."""
     import numpy as np
@@ -736,20 +775,26 @@ def run_design(args):
     sampler.start()
     t0 = time.monotonic()
     out = []
-    dup, fut = args.design == "dupolorn", args.design == "futidra"
-    sizes = FUTIDRA_SIZES if fut else (DUPOLORN_SIZES if dup else DESIGN_SIZES)
+    dup, fut, rud = args.design == "dupolorn", args.design == "futidra", args.design == "rudolix"
+    sizes = RUDOLIX_SIZES if rud else (FUTIDRA_SIZES if fut else (DUPOLORN_SIZES if dup else DESIGN_SIZES))
     names = [n for n in sizes if args.design_size in ("all", n)]
     for name in names:
         z = sizes[name]
         if fut:
             z = dict(z, experts=1, top=1, groups=1, keep=1)
+        if rud:
+            z = dict(z, groups=1, keep=1)
         rot = Cf.RotarySpec(base=10000.0, dims=z["dim"], factor=4.0, original=4096, fast=32.0, slow=1.0, scaled=True)
         att = Cf.AttentionSpec(heads=z["heads"], kv_heads=z["kv"], dim=z["dim"], vdim=z["dim"], scale=z["dim"] ** -0.5, rot=rot,
                                value_rot=Cf.RotarySpec(base=10000.0, dims=z["dim"]))
         moe = Cf.MoESpec(experts=z["experts"], top=z["top"], ff=z["ff"], groups=z["groups"], keep=z["keep"])
+        if rud:
+            z = {k: v for k, v in z.items() if k not in ("groups", "keep")}
         arms = {"bopilorn": Cf.BopilornConfig(name=name, width=z["width"], vocab=z["vocab"], embed_scale=1.0,
                                               layers=[Cf.StackLayerSpec(mixer=att, mlp=moe) for _ in range(z["layers"])])}
-        if fut:
+        if rud:
+            arms = {"rudolix": _rudolix_config(Cf, name, z), "futidra": _futidra_like_rudolix(Cf, name, z)}
+        elif fut:
             arms = {"futidra": _futidra_config(Cf, name, z), "dupolorn": _dupolorn_dense_config(Cf, name, z)}
         elif dup:
             arms = {"dupolorn": _dupolorn_config(Cf, name, z), "bopilorn": arms["bopilorn"]}
@@ -777,8 +822,9 @@ def run_design(args):
             torch.cuda.empty_cache()
         out.append(rec)
     clocks = sampler.stop(t0, time.monotonic())
-    emit({"metric": "design_compare", "design": "Futidra" if fut else ("Dupolorn" if dup else "Bopilorn"),
-          "closest": "dupolorn with dense feed-forwards (latent attention, matrix-memory recurrence, state slots)" if fut else
+    emit({"metric": "design_compare", "design": "Rudolix" if rud else ("Futidra" if fut else ("Dupolorn" if dup else "Bopilorn")),
+          "closest": "futidra (attention with a value cache, delta rule on the same scan, state slots, dense feed-forwards)" if rud else
+                     "dupolorn with dense feed-forwards (latent attention, matrix-memory recurrence, state slots)" if fut else
                      ("bopilorn (layer-list model with routed experts)" if dup else "llama (fixed decoder stack)"), "dtype": "bf16",
           "data": "synthetic, random-init weights", "steps": K, "warmup": W, "l2": "flushed between steps (512 MiB written)",
           "sizes": out, "clocks": clocks})
@@ -793,10 +839,10 @@ def main():
     ap.add_argument("--workload", default="llama8b-bs64", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--headline-only", action="store_true", help="skip the `also` and `tp` sections of the default run")
-    ap.add_argument("--design", default=None, choices=["bopilorn", "dupolorn", "futidra"],
+    ap.add_argument("--design", default=None, choices=["bopilorn", "dupolorn", "futidra", "rudolix"],
                     help="instead of the default workload: prefill / decode throughput of this design beside the closest fixed-stack "
                          "model at equal size")
-    ap.add_argument("--design-size", default="all", choices=["all"] + sorted(set(DESIGN_SIZES) | set(DUPOLORN_SIZES) | set(FUTIDRA_SIZES)))
+    ap.add_argument("--design-size", default="all", choices=["all"] + sorted(set(DESIGN_SIZES) | set(DUPOLORN_SIZES) | set(FUTIDRA_SIZES) | set(RUDOLIX_SIZES)))
     args = ap.parse_args()
     claim_stdout()
     if args.design:

@@ -409,7 +409,11 @@ int ssd_gate_norm(bool f32, const float* o, const float* xn, const float* skip, 
 // multi-stream pre-norm layer form (hyper.cu)
 int hyper_step(bool f32, float* X, int64_t sstride, int n, bool init, const void* y, const float* parts, int n_parts, const float* scale,
                const float* hc, float mult, const float* open_in, const float* nw, const float* nb, float eps, const int32_t* rows,
-               float* h_f32, void* h_act, float* sum_out, int R, int width, cudaStream_t s);
+               float* h_f32, void* h_act, float* sum_out, int R, int width, cudaStream_t s, const float* conv_w = nullptr, int taps = 0,
+               const int32_t* positions = nullptr, const int32_t* row_to_seq = nullptr, const int32_t* seq_slots = nullptr,
+               float* tails = nullptr, int64_t slot_stride = 0);
+// conv_w [width][taps] given (steps whose sequences bring one row each): h + conv(h) goes to h_act and the tails
+// [slot][taps - 1][width] (slot_stride floats apart) are shifted by the row
 int qkv_rotate_cache(bool f32, const void* qkv, int64_t ld, const int32_t* positions, const int32_t* slots, const float* rot, int rot_dims,
                      bool half_layout, int64_t max_pos, float* qout, void* kc, void* vc, int T, int heads, int kv_heads, int dim, int vdim,
                      int block_size, cudaStream_t s);

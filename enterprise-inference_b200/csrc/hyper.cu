@@ -5,12 +5,15 @@
 //    Streams are elementwise in the channel, so a thread keeps the n values of its channels in registers; only u is
 //    staged (one row in shared memory) for the two statistics passes.  The first launch of a step copies stream 0 (the
 //    scaled embedding) into every stream; the last one runs over the logit rows only, with a = ones and the output norm.
-//    y is an activation row or the sum, in slot order, of n_parts fp32 partial rows (routed experts).
+//    y is an activation row or the sum, in slot order, of n_parts fp32 partial rows (routed experts).  A step whose sequences
+//    bring one row each (decode) also runs the input convolution here: its earlier taps are the tail in the state slot.
 //  * qkv_rotate_cache: plain q | k | v projections; the leading rot_dims dimensions of every q and k head turn by the
 //    angles of an fp32 cos|sin table, dimension i paired with i + rot_dims / 2 (half layout) or 2i with 2i + 1; q leaves
 //    as fp32 rows, k and v go to the paged caches.
 //  * polynorm: p(z) = c0 N(z) + c1 N(z^2) + c2 N(z^3) + c3 over the ff entries of a token, N(v) = v / sqrt(mean(v^2) + eps);
 //    the three mean squares come from one pass over the row (z^2, z^4, z^6), all in fp32.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace b200 {
@@ -25,100 +28,178 @@ template <> __device__ __forceinline__ void stx<__nv_bfloat16>(__nv_bfloat16* p,
 
 constexpr int kHyThreads = 256;
 constexpr int kMaxN = B200_MAX_STREAMS;
+constexpr int kHyMaxTaps = 16;
 
+// sum over the CTA (any number of warps up to 32)
 __device__ __forceinline__ float block_sum_hy(float v, float* red) {
   v = warp_sum(v);
+  const int nw = (blockDim.x + 31) >> 5;
   __syncthreads();
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
   __syncthreads();
   float a = 0.f;
-#pragma unroll
-  for (int i = 0; i < kHyThreads / 32; ++i) a += red[i];
+  for (int i = 0; i < nw; ++i) a += red[i];
   return a;
 }
 
-template <typename AT, int N>
-__global__ void __launch_bounds__(kHyThreads)
+template <typename AT, int V> __device__ __forceinline__ void ldv(const AT* p, int64_t i, float* o);
+template <> __device__ __forceinline__ void ldv<float, 1>(const float* p, int64_t i, float* o) { o[0] = p[i]; }
+template <> __device__ __forceinline__ void ldv<__nv_bfloat16, 1>(const __nv_bfloat16* p, int64_t i, float* o) { o[0] = __bfloat162float(p[i]); }
+template <> __device__ __forceinline__ void ldv<float, 4>(const float* p, int64_t i, float* o) {
+  const float4 v = *reinterpret_cast<const float4*>(p + i);
+  o[0] = v.x, o[1] = v.y, o[2] = v.z, o[3] = v.w;
+}
+template <> __device__ __forceinline__ void ldv<__nv_bfloat16, 4>(const __nv_bfloat16* p, int64_t i, float* o) {
+  const uint2 v = *reinterpret_cast<const uint2*>(p + i);
+  o[0] = bf16lo(v.x), o[1] = bf16hi(v.x), o[2] = bf16lo(v.y), o[3] = bf16hi(v.y);
+}
+template <typename AT, int V> __device__ __forceinline__ void stv(AT* p, int64_t i, const float* o);
+template <> __device__ __forceinline__ void stv<float, 1>(float* p, int64_t i, const float* o) { p[i] = o[0]; }
+template <> __device__ __forceinline__ void stv<__nv_bfloat16, 1>(__nv_bfloat16* p, int64_t i, const float* o) { p[i] = __float2bfloat16_rn(o[0]); }
+template <> __device__ __forceinline__ void stv<float, 4>(float* p, int64_t i, const float* o) {
+  *reinterpret_cast<float4*>(p + i) = make_float4(o[0], o[1], o[2], o[3]);
+}
+template <> __device__ __forceinline__ void stv<__nv_bfloat16, 4>(__nv_bfloat16* p, int64_t i, const float* o) {
+  *reinterpret_cast<uint2*>(p + i) = make_uint2(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]));
+}
+
+// The input convolution of a step whose sequences bring ONE row each (decode steps), fused behind the norm: the taps before
+// the row's own come from the sequence's tail in its state slot, which is shifted by one place and takes the row.
+struct HyperConv {
+  const float* w = nullptr;            // [width][taps]; nullptr: no fused convolution
+  int taps = 0;
+  const int32_t* positions = nullptr;
+  const int32_t* row_to_seq = nullptr;
+  const int32_t* seq_slots = nullptr;
+  float* tails = nullptr;              // this sublayer's tail of slot 0: [taps - 1][width]
+  int64_t slot_stride = 0;
+};
+
+// V channels per thread and trip (4: 16-byte accesses; the row length and every pointer then are multiples of 4 floats)
+template <typename AT, int N, int V>
+__global__ void __launch_bounds__(1024)
 hyper_step_kernel(float* X, int64_t sstride, int init, const AT* __restrict__ y, const float* __restrict__ parts, int n_parts,
                   const float* __restrict__ scale, const float* __restrict__ hc, float mult, const float* __restrict__ open_in,
                   const float* __restrict__ nw, const float* __restrict__ nb, float eps, const int32_t* __restrict__ rows,
-                  float* __restrict__ h_f32, AT* __restrict__ h_act, float* __restrict__ sum_out, int width) {
-  extern __shared__ float hy_row[];
-  __shared__ float red[kHyThreads / 32];
+                  float* __restrict__ h_f32, AT* __restrict__ h_act, float* __restrict__ sum_out, int width, HyperConv cv) {
+  extern __shared__ __align__(16) float hy_row[];
+  __shared__ float red[32];
   __shared__ float coef[2 * kMaxN + kMaxN * kMaxN + kMaxN];   // a | b | M of the closing sublayer, then the opening a
   pdl_wait();
   pdl_launch_dependents();
   const int64_t t = blockIdx.x;
   const int64_t src = rows ? (int64_t)rows[t] : t;
-  if (threadIdx.x < 2 * N + N * N) coef[threadIdx.x] = hc ? hc[threadIdx.x] : 0.f;
+  const int nt = blockDim.x;
+  for (int i = threadIdx.x; i < 2 * N + N * N; i += nt) coef[i] = hc ? hc[i] : 0.f;
   if (threadIdx.x < N) coef[2 * N + N * N + threadIdx.x] = open_in ? open_in[threadIdx.x] : 1.0f;
   __syncthreads();
   const float* cb = coef + N;
   const float* cm = coef + 2 * N;
   const float* ca = coef + 2 * N + N * N;
   float sum = 0.f;
-  for (int c = threadIdx.x; c < width; c += kHyThreads) {
-    float xs[N], xn[N];
+  for (int c = threadIdx.x * V; c < width; c += nt * V) {
+    float xs[N][V], u[V], all[V];
 #pragma unroll
-    for (int s = 0; s < N; ++s) xs[s] = X[(init ? 0 : s) * sstride + src * width + c];
+    for (int s = 0; s < N; ++s) ldv<float, V>(X, (init ? 0 : s) * sstride + src * width + c, xs[s]);
+#pragma unroll
+    for (int v = 0; v < V; ++v) u[v] = all[v] = 0.f;
     if (hc) {
-      float yv;
+      float yv[V];
       if (y) {
-        yv = ldx<AT>(y, src * width + c);
+        ldv<AT, V>(y, src * width + c, yv);
       } else {
-        yv = 0.f;
-        for (int j = 0; j < n_parts; ++j) yv += parts[(src * n_parts + j) * width + c];
+#pragma unroll
+        for (int v = 0; v < V; ++v) yv[v] = 0.f;
+        for (int j = 0; j < n_parts; ++j) {
+          float pv[V];
+          ldv<float, V>(parts, (src * n_parts + j) * width + c, pv);
+#pragma unroll
+          for (int v = 0; v < V; ++v) yv[v] += pv[v];
+        }
       }
-      yv = yv * scale[c] * mult;
+      float sc[V];
+      ldv<float, V>(scale, c, sc);
+#pragma unroll
+      for (int v = 0; v < V; ++v) yv[v] = yv[v] * sc[v] * mult;
 #pragma unroll
       for (int q = 0; q < N; ++q) {
-        float a = 0.f;
+        float a[V];
 #pragma unroll
-        for (int s = 0; s < N; ++s) a = fmaf(cm[s * N + q], xs[s], a);
-        xn[q] = fmaf(cb[q], yv, a);
-      }
-      if (!rows) {
+        for (int v = 0; v < V; ++v) {
+          float acc = 0.f;
 #pragma unroll
-        for (int q = 0; q < N; ++q) X[q * sstride + src * width + c] = xn[q];
+          for (int s = 0; s < N; ++s) acc = fmaf(cm[s * N + q], xs[s][v], acc);
+          a[v] = fmaf(cb[q], yv[v], acc);
+          u[v] = fmaf(ca[q], a[v], u[v]);
+          all[v] += a[v];
+        }
+        if (!rows) stv<float, V>(X, q * sstride + src * width + c, a);
       }
     } else {
 #pragma unroll
-      for (int q = 0; q < N; ++q) xn[q] = xs[q];
-      if (init && !rows) {
+      for (int q = 0; q < N; ++q) {
 #pragma unroll
-        for (int q = 1; q < N; ++q) X[q * sstride + src * width + c] = xn[q];
+        for (int v = 0; v < V; ++v) {
+          u[v] = fmaf(ca[q], xs[q][v], u[v]);
+          all[v] += xs[q][v];
+        }
+        if (init && !rows && q > 0) stv<float, V>(X, q * sstride + src * width + c, xs[q]);
       }
     }
-    float u = 0.f, all = 0.f;
+    if (sum_out) stv<float, V>(sum_out, t * width + c, all);
+    stv<float, V>(hy_row, c, u);
 #pragma unroll
-    for (int q = 0; q < N; ++q) {
-      u = fmaf(ca[q], xn[q], u);
-      all += xn[q];
-    }
-    if (sum_out) sum_out[t * width + c] = all;
-    hy_row[c] = u;
-    sum += u;
+    for (int v = 0; v < V; ++v) sum += u[v];
   }
   if (!h_f32 && !h_act) return;
   if (!nw) {
     __syncthreads();
-    for (int c = threadIdx.x; c < width; c += kHyThreads) {
+    for (int c = threadIdx.x; c < width; c += nt) {
       if (h_f32) h_f32[t * width + c] = hy_row[c];
-      if (h_act) stx<AT>(h_act, t * width + c, hy_row[c]);
+      if (h_act) stv<AT, 1>(h_act, t * width + c, hy_row + c);
     }
     return;
   }
   const float mean = block_sum_hy(sum, red) / (float)width;
   float sq = 0.f;
-  for (int c = threadIdx.x; c < width; c += kHyThreads) {
-    const float d = hy_row[c] - mean;
-    sq = fmaf(d, d, sq);
+  for (int c = threadIdx.x * V; c < width; c += nt * V) {
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+      const float d = hy_row[c + v] - mean;
+      sq = fmaf(d, d, sq);
+    }
   }
   const float rstd = 1.0f / sqrtf(block_sum_hy(sq, red) / (float)width + eps);
-  for (int c = threadIdx.x; c < width; c += kHyThreads) {
-    const float v = (hy_row[c] - mean) * rstd * nw[c] + (nb ? nb[c] : 0.f);
-    if (h_f32) h_f32[t * width + c] = v;
-    if (h_act) stx<AT>(h_act, t * width + c, v);
+  if (cv.w == nullptr) {
+    for (int c = threadIdx.x * V; c < width; c += nt * V) {
+      float wv[V], bv[V], o[V];
+      ldv<float, V>(nw, c, wv);
+      if (nb) ldv<float, V>(nb, c, bv);
+#pragma unroll
+      for (int v = 0; v < V; ++v) o[v] = (hy_row[c + v] - mean) * rstd * wv[v] + (nb ? bv[v] : 0.f);
+      if (h_f32) stv<float, V>(h_f32, t * width + c, o);
+      if (h_act) stv<AT, V>(h_act, t * width + c, o);
+    }
+    return;
+  }
+  // one row per sequence: out = h + sum_j w[:, j] in_j with in_(taps-1) = h and the earlier inputs from the tail
+  const int s = cv.row_to_seq ? cv.row_to_seq[t] : (int)t;
+  const int hist = cv.taps - 1, p0 = cv.positions[t];
+  float* tail = hist ? cv.tails + (int64_t)cv.seq_slots[s] * cv.slot_stride : nullptr;
+  for (int c = threadIdx.x; c < width; c += nt) {
+    const float h = (hy_row[c] - mean) * rstd * nw[c] + (nb ? nb[c] : 0.f);
+    float old[kHyMaxTaps];
+#pragma unroll
+    for (int i = 0; i < kHyMaxTaps; ++i) old[i] = (i < hist && p0 - hist + i >= 0) ? tail[(int64_t)i * width + c] : 0.f;
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < kHyMaxTaps; ++j)
+      if (j < cv.taps) acc = fmaf(cv.w[c * cv.taps + j], j == hist ? h : old[j], acc);
+    const float o = h + acc;
+    stv<AT, 1>(h_act, t * width + c, &o);
+#pragma unroll
+    for (int i = 0; i < kHyMaxTaps; ++i)
+      if (i < hist) tail[(int64_t)i * width + c] = i + 1 < hist ? old[i + 1] : h;
   }
 }
 
@@ -203,21 +284,33 @@ polynorm_kernel(const AT* __restrict__ z, const float* __restrict__ coef, AT* __
 template <typename AT, int N>
 int hyper_step_n(float* X, int64_t sstride, int init, const void* y, const float* parts, int n_parts, const float* scale, const float* hc,
                  float mult, const float* open_in, const float* nw, const float* nb, float eps, const int32_t* rows, float* h_f32, void* h_act,
-                 float* sum_out, int R, int width, cudaStream_t s) {
+                 float* sum_out, int R, int width, const HyperConv& cv, cudaStream_t s) {
   const size_t smem = (size_t)width * 4;
-  static bool done[64] = {};
-  if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(hyper_step_kernel<AT, N>, 200 * 1024, done));
-  B200_CUDA(launch(hyper_step_kernel<AT, N>, dim3(R), dim3(kHyThreads), smem, s, X, sstride, init, (const AT*)y, parts, n_parts, scale, hc, mult,
-                   open_in, nw, nb, eps, rows, h_f32, (AT*)h_act, sum_out, width));
+  const uintptr_t ptrs = reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(parts) |
+                         reinterpret_cast<uintptr_t>(scale) | reinterpret_cast<uintptr_t>(nw) | reinterpret_cast<uintptr_t>(nb) |
+                         reinterpret_cast<uintptr_t>(h_f32) | reinterpret_cast<uintptr_t>(h_act) | reinterpret_cast<uintptr_t>(sum_out);
+  if (N <= 4 && width % 4 == 0 && sstride % 4 == 0 && ptrs % 16 == 0) {
+    const int threads = std::min(1024, std::max(128, (width / 4 + 31) / 32 * 32));
+    static bool done[64] = {};
+    if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(hyper_step_kernel<AT, N, 4>, 200 * 1024, done));
+    B200_CUDA(launch(hyper_step_kernel<AT, N, 4>, dim3(R), dim3(threads), smem, s, X, sstride, init, (const AT*)y, parts, n_parts, scale, hc, mult,
+                     open_in, nw, nb, eps, rows, h_f32, (AT*)h_act, sum_out, width, cv));
+    return B200_OK;
+  }
+  const int threads = std::min(1024, std::max(128, (width / 2 + 31) / 32 * 32));
+  static bool done1[64] = {};
+  if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(hyper_step_kernel<AT, N, 1>, 200 * 1024, done1));
+  B200_CUDA(launch(hyper_step_kernel<AT, N, 1>, dim3(R), dim3(threads), smem, s, X, sstride, init, (const AT*)y, parts, n_parts, scale, hc, mult,
+                   open_in, nw, nb, eps, rows, h_f32, (AT*)h_act, sum_out, width, cv));
   return B200_OK;
 }
 
 template <typename AT>
 int hyper_step_t(int n, float* X, int64_t sstride, int init, const void* y, const float* parts, int n_parts, const float* scale, const float* hc,
                  float mult, const float* open_in, const float* nw, const float* nb, float eps, const int32_t* rows, float* h_f32, void* h_act,
-                 float* sum_out, int R, int width, cudaStream_t s) {
+                 float* sum_out, int R, int width, const HyperConv& cv, cudaStream_t s) {
 #define HY(N) \
-  case N: return hyper_step_n<AT, N>(X, sstride, init, y, parts, n_parts, scale, hc, mult, open_in, nw, nb, eps, rows, h_f32, h_act, sum_out, R, width, s)
+  case N: return hyper_step_n<AT, N>(X, sstride, init, y, parts, n_parts, scale, hc, mult, open_in, nw, nb, eps, rows, h_f32, h_act, sum_out, R, width, cv, s)
   switch (n) {
     HY(1);
     HY(2);
@@ -236,15 +329,23 @@ int hyper_step_t(int n, float* X, int64_t sstride, int init, const void* y, cons
 
 int hyper_step(bool f32, float* X, int64_t sstride, int n, bool init, const void* y, const float* parts, int n_parts, const float* scale,
                const float* hc, float mult, const float* open_in, const float* nw, const float* nb, float eps, const int32_t* rows,
-               float* h_f32, void* h_act, float* sum_out, int R, int width, cudaStream_t s) {
+               float* h_f32, void* h_act, float* sum_out, int R, int width, cudaStream_t s, const float* conv_w, int taps,
+               const int32_t* positions, const int32_t* row_to_seq, const int32_t* seq_slots, float* tails, int64_t slot_stride) {
   if (R == 0) return B200_OK;
   B200_REQUIRE(X && n >= 1 && n <= kMaxN, B200_ERR_INVALID, "hyper_step: %d streams outside [1, %d]", n, kMaxN);
   B200_REQUIRE(!hc || ((y || (parts && n_parts > 0)) && scale), B200_ERR_INVALID, "hyper_step: a closing sublayer needs its result and its scale");
   B200_REQUIRE((size_t)width * 4 <= 200 * 1024, B200_ERR_UNSUPPORTED, "hyper_step: width %d does not fit shared memory", width);
+  HyperConv cv;
+  if (conv_w) {
+    B200_REQUIRE(taps >= 1 && taps <= kHyMaxTaps && nw && h_act && !rows && positions && (taps == 1 || (seq_slots && tails)), B200_ERR_INVALID,
+                 "hyper_step: the fused convolution needs 1 to %d taps, a norm, an output, positions and the tails", kHyMaxTaps);
+    cv.w = conv_w, cv.taps = taps, cv.positions = positions, cv.row_to_seq = row_to_seq, cv.seq_slots = seq_slots, cv.tails = tails;
+    cv.slot_stride = slot_stride;
+  }
   return f32 ? hyper_step_t<float>(n, X, sstride, init ? 1 : 0, y, parts, n_parts, scale, hc, mult, open_in, nw, nb, eps, rows, h_f32, h_act,
-                                   sum_out, R, width, s)
+                                   sum_out, R, width, cv, s)
              : hyper_step_t<__nv_bfloat16>(n, X, sstride, init ? 1 : 0, y, parts, n_parts, scale, hc, mult, open_in, nw, nb, eps, rows, h_f32,
-                                           h_act, sum_out, R, width, s);
+                                           h_act, sum_out, R, width, cv, s);
 }
 
 int qkv_rotate_cache(bool f32, const void* qkv, int64_t ld, const int32_t* positions, const int32_t* slots, const float* rot, int rot_dims,

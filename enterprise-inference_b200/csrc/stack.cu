@@ -625,7 +625,17 @@ static int stack_enqueue_step_hyper(b200_ctx* c, const StepArgs& a, cudaStream_t
   int n_parts_prev = 0;
   bool first = true;
   // closes the sublayer before, opens one with coefficients hc / norm (w, b) / convolution cw (tail at tail_off) into `out`
+  // every sequence brings one row (decode): the convolution runs behind the norm in the same launch
+  static const int fuse_env = getenv("B200_STACK_FUSE_CANON") ? atoi(getenv("B200_STACK_FUSE_CANON")) : 1;
+  const bool conv_fused = conv && fuse_env && S == T && (m.canon_taps == 1 || M->state);
   auto open = [&](const float* hc, const float* w, const float* b, const float* cw, int64_t tail_off, void* out, float* tap) -> int {
+    if (conv_fused) {
+      const bool was_first = first;
+      first = false;
+      return hyper_step(f32, X, sstride, n, was_first, y_prev, parts_prev, n_parts_prev, scale_prev, hc_prev, m.residual_mult, hc, w, b, m.norm_eps,
+                        nullptr, nullptr, out, tap, T, Wd, s, cw, m.canon_taps, a.positions, a.row_to_seq, seq_slots,
+                        M->state ? M->state + tail_off : nullptr, M->slot_floats);
+    }
     int r = hyper_step(f32, X, sstride, n, first, y_prev, parts_prev, n_parts_prev, scale_prev, hc_prev, m.residual_mult, hc, w, b, m.norm_eps,
                        nullptr, conv ? M->h1f : nullptr, conv ? nullptr : out, tap, T, Wd, s);
     first = false;

@@ -150,18 +150,20 @@ parallel_close_kernel(float* __restrict__ u, const AT* __restrict__ y_mix, const
 // hc[t] = h[t] + sum_j w[:, j] * h[t - taps + 1 + j] along each sequence (zeros before position 0).  Rows whose window
 // stays inside the step's portion of the sequence are one CTA each.  The first row of a portion also serves the next
 // taps - 2 rows (those whose window reaches into the state slot's tail), then writes the new tail: every read of the old
-// tail happens in the one CTA that overwrites it.
+// tail happens in the one CTA that overwrites it.  Long steps give a CTA several consecutive rows (rows_per_cta): a row's
+// CTA starts with three dependent lookups (sequence, bounds, position), which one CTA per row pays once per row.
 constexpr int kMaxTaps = 16;
 template <typename AT>
 __global__ void __launch_bounds__(256)
 canon_conv_kernel(const float* __restrict__ h, const float* __restrict__ w, AT* __restrict__ out, int width, int taps,
                   const int32_t* __restrict__ positions, const int32_t* __restrict__ row_to_seq, const int32_t* __restrict__ seq_start,
-                  const int32_t* __restrict__ seq_slots, float* __restrict__ tails, int64_t slot_stride) {
+                  const int32_t* __restrict__ seq_slots, float* __restrict__ tails, int64_t slot_stride, int T, int rows_per_cta) {
   pdl_wait();
   pdl_launch_dependents();
-  const int t = blockIdx.x;
-  const int s = row_to_seq ? row_to_seq[t] : t;
   const int hist = taps - 1;
+  const int t_end = min(T, (int)(blockIdx.x + 1) * rows_per_cta);
+  for (int t = blockIdx.x * rows_per_cta; t < t_end; ++t) {
+  const int s = row_to_seq ? row_to_seq[t] : t;
   const int start = hist ? seq_start[s] : t, n = hist ? seq_start[s + 1] - start : 1, r = t - start;
   if (r >= hist) {
     for (int c = blockIdx.y * 256 + threadIdx.x; c < width; c += gridDim.y * 256) {
@@ -170,9 +172,9 @@ canon_conv_kernel(const float* __restrict__ h, const float* __restrict__ w, AT* 
       for (int j = 0; j < taps; ++j) acc = fmaf(w[c * taps + j], h[(int64_t)(t - hist + j) * width + c], acc);
       stx<AT>(out, (int64_t)t * width + c, a + acc);
     }
-    return;
+    continue;
   }
-  if (r != 0) return;
+  if (r != 0) continue;
   const int p0 = positions[t];
   float* tail = tails + (int64_t)seq_slots[s] * slot_stride;   // [hist][width]: inputs at positions p0 - hist .. p0 - 1
   for (int c = blockIdx.y * 256 + threadIdx.x; c < width; c += gridDim.y * 256) {
@@ -201,6 +203,7 @@ canon_conv_kernel(const float* __restrict__ h, const float* __restrict__ w, AT* 
     }
     for (int i = 0; i < hist; ++i) tail[(int64_t)i * width + c] = at(n - hist + i);
   }
+  }
 }
 
 template <typename AT>
@@ -223,12 +226,35 @@ rms_rows_kernel(const float* __restrict__ u, const int32_t* __restrict__ rows, c
   for (int c = threadIdx.x; c < width; c += 256) stx<AT>(out, dst + c, row[c] * a);
 }
 
+// two neighbours at an even index in one access
+__device__ __forceinline__ void ld2(const float* p, int64_t i, float& a, float& b) {
+  const float2 v = *reinterpret_cast<const float2*>(p + i);
+  a = v.x, b = v.y;
+}
+__device__ __forceinline__ void ld2(const __nv_bfloat16* p, int64_t i, float& a, float& b) {
+  const uint32_t v = *reinterpret_cast<const uint32_t*>(p + i);
+  a = bf16lo(v), b = bf16hi(v);
+}
+__device__ __forceinline__ void st2(float* p, int64_t i, float a, float b) { *reinterpret_cast<float2*>(p + i) = make_float2(a, b); }
+__device__ __forceinline__ void st2(__nv_bfloat16* p, int64_t i, float a, float b) { *reinterpret_cast<uint32_t*>(p + i) = pack_bf16(a, b); }
+
 // gated: out[t][f] = act(in[t][f]) * in[t][ff + f] over rows of 2 ff; plain: out[t][f] = act(in[t][f]) (in place allowed)
 template <typename AT>
 __global__ void __launch_bounds__(256)
 ff_act_kernel(const AT* __restrict__ in, AT* __restrict__ out, int64_t total, int ff, int gated, int kind, float limit) {
   pdl_wait();
   pdl_launch_dependents();
+  if (gated && ff % 2 == 0 && (reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) % 8 == 0) {   // two neighbours per thread and trip
+    const int64_t rows = total / ff, pairs = ff >> 1, n2 = rows * pairs;
+    for (int64_t i = blockIdx.x * 256ll + threadIdx.x; i < n2; i += gridDim.x * 256ll) {
+      const int64_t t = i / pairs, f = (i - t * pairs) * 2;
+      float g0, g1, u0, u1;
+      ld2(in, t * 2 * ff + f, g0, g1);
+      ld2(in, t * 2 * ff + ff + f, u0, u1);
+      st2(out, t * ff + f, gate_combine(g0, u0, kind, limit), gate_combine(g1, u1, kind, limit));
+    }
+    return;
+  }
   for (int64_t i = blockIdx.x * 256ll + threadIdx.x; i < total; i += gridDim.x * 256ll) {
     if (gated) {
       const int64_t t = i / ff, f = i % ff;
@@ -312,12 +338,14 @@ int canon_conv(bool f32, const float* h, const float* w, void* out, int T, int w
   if (T == 0) return B200_OK;
   B200_REQUIRE(taps >= 1 && taps <= kMaxTaps, B200_ERR_UNSUPPORTED, "canon_conv: %d taps outside [1, %d]", taps, kMaxTaps);
   B200_REQUIRE(taps == 1 || (positions && seq_start && seq_slots && tails), B200_ERR_INVALID, "canon_conv: null argument");
+  const int rpc = T >= 1024 ? 8 : (T >= 256 ? 4 : 1);
+  const dim3 grid((T + rpc - 1) / rpc, (width + 255) / 256);
   if (f32)
-    B200_CUDA(launch(canon_conv_kernel<float>, dim3(T, (width + 255) / 256), dim3(256), (size_t)0, s, h, w, (float*)out, width, taps, positions, row_to_seq,
-                     seq_start, seq_slots, tails, slot_stride));
+    B200_CUDA(launch(canon_conv_kernel<float>, grid, dim3(256), (size_t)0, s, h, w, (float*)out, width, taps, positions, row_to_seq,
+                     seq_start, seq_slots, tails, slot_stride, T, rpc));
   else
-    B200_CUDA(launch(canon_conv_kernel<__nv_bfloat16>, dim3(T, (width + 255) / 256), dim3(256), (size_t)0, s, h, w, (__nv_bfloat16*)out, width, taps,
-                     positions, row_to_seq, seq_start, seq_slots, tails, slot_stride));
+    B200_CUDA(launch(canon_conv_kernel<__nv_bfloat16>, grid, dim3(256), (size_t)0, s, h, w, (__nv_bfloat16*)out, width, taps,
+                     positions, row_to_seq, seq_start, seq_slots, tails, slot_stride, T, rpc));
   return B200_OK;
 }
 
