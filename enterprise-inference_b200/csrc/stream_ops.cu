@@ -206,6 +206,74 @@ canon_conv_kernel(const float* __restrict__ h, const float* __restrict__ w, AT* 
   }
 }
 
+// The same for a known number of taps: a thread owns one channel over a run of consecutive rows and keeps the last TAPS - 1
+// inputs in registers, so every input is fetched once instead of TAPS times.  A row at least TAPS - 1 places into its
+// portion reads nothing but the rows before it in the step's buffer, whatever sequence those first rows of the run belong
+// to; the first row of a portion takes the path through the tail as above.
+constexpr int kConvRun = 16;
+template <typename AT, int TAPS>
+__global__ void __launch_bounds__(256)
+canon_conv_run_kernel(const float* __restrict__ h, const float* __restrict__ w, AT* __restrict__ out, int width,
+                      const int32_t* __restrict__ positions, const int32_t* __restrict__ row_to_seq, const int32_t* __restrict__ seq_start,
+                      const int32_t* __restrict__ seq_slots, float* __restrict__ tails, int64_t slot_stride, int T) {
+  constexpr int H = TAPS - 1;
+  __shared__ int row_r[kConvRun], row_s[kConvRun];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t0 = blockIdx.x * kConvRun, t1 = min(T, t0 + kConvRun);
+  if (threadIdx.x < t1 - t0) {
+    const int t = t0 + threadIdx.x;
+    const int s = row_to_seq ? row_to_seq[t] : t;
+    row_s[threadIdx.x] = s;
+    row_r[threadIdx.x] = H ? t - seq_start[s] : 0;
+  }
+  __syncthreads();
+  const int c = blockIdx.y * 256 + threadIdx.x;
+  if (c >= width) return;
+  float wv[TAPS], win[H > 0 ? H : 1];
+#pragma unroll
+  for (int j = 0; j < TAPS; ++j) wv[j] = w[c * TAPS + j];
+#pragma unroll
+  for (int j = 0; j < H; ++j) win[j] = t0 - H + j >= 0 ? h[(int64_t)(t0 - H + j) * width + c] : 0.f;
+  for (int t = t0; t < t1; ++t) {
+    const float cur = h[(int64_t)t * width + c];
+    const int r = row_r[t - t0];
+    if (r >= H) {
+      float acc = 0.f;
+#pragma unroll
+      for (int j = 0; j < H; ++j) acc = fmaf(wv[j], win[j], acc);
+      acc = fmaf(wv[H], cur, acc);
+      stx<AT>(out, (int64_t)t * width + c, cur + acc);
+    } else if (r == 0) {
+      const int s = row_s[t - t0], n = seq_start[s + 1] - t, p0 = positions[t];
+      float* tail = tails + (int64_t)seq_slots[s] * slot_stride;   // [H][width]: inputs at positions p0 - H .. p0 - 1
+      float old[H > 0 ? H : 1];
+#pragma unroll
+      for (int i = 0; i < H; ++i) old[i] = p0 - H + i >= 0 ? tail[(int64_t)i * width + c] : 0.f;
+      auto at = [&](int o) -> float {   // the input at offset o from the portion's first row (o < 0: the tail)
+        if (o >= 0) return h[(int64_t)(t + o) * width + c];
+        float v = 0.f;
+#pragma unroll
+        for (int i = 0; i < H; ++i)
+          if (i == H + o) v = old[i];
+        return v;
+      };
+      const int head_rows = n < H ? n : H;
+      for (int rr = 0; rr < head_rows; ++rr) {
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) acc = fmaf(wv[j], at(rr - H + j), acc);
+        stx<AT>(out, (int64_t)(t + rr) * width + c, at(rr) + acc);
+      }
+#pragma unroll
+      for (int i = 0; i < H; ++i) tail[(int64_t)i * width + c] = at(n - H + i);
+    }
+#pragma unroll
+    for (int j = 0; j + 1 < H; ++j) win[j] = win[j + 1];
+    if (H > 0) win[H - 1] = cur;
+  }
+}
+
 template <typename AT>
 __global__ void __launch_bounds__(256)
 rms_rows_kernel(const float* __restrict__ u, const int32_t* __restrict__ rows, const float* __restrict__ g, AT* __restrict__ out,
@@ -338,7 +406,30 @@ int canon_conv(bool f32, const float* h, const float* w, void* out, int T, int w
   if (T == 0) return B200_OK;
   B200_REQUIRE(taps >= 1 && taps <= kMaxTaps, B200_ERR_UNSUPPORTED, "canon_conv: %d taps outside [1, %d]", taps, kMaxTaps);
   B200_REQUIRE(taps == 1 || (positions && seq_start && seq_slots && tails), B200_ERR_INVALID, "canon_conv: null argument");
-  const int rpc = T >= 1024 ? 8 : (T >= 256 ? 4 : 1);
+  if (taps <= 8 && T >= 64) {   // long steps: runs of rows with the window in registers
+    const dim3 rgrid((T + kConvRun - 1) / kConvRun, (width + 255) / 256);
+#define CONV_RUN(N)                                                                                                                         \
+  case N:                                                                                                                                   \
+    if (f32)                                                                                                                                \
+      B200_CUDA(launch(canon_conv_run_kernel<float, N>, rgrid, dim3(256), (size_t)0, s, h, w, (float*)out, width, positions, row_to_seq,    \
+                       seq_start, seq_slots, tails, slot_stride, T));                                                                       \
+    else                                                                                                                                    \
+      B200_CUDA(launch(canon_conv_run_kernel<__nv_bfloat16, N>, rgrid, dim3(256), (size_t)0, s, h, w, (__nv_bfloat16*)out, width, positions, \
+                       row_to_seq, seq_start, seq_slots, tails, slot_stride, T));                                                           \
+    return B200_OK;
+    switch (taps) {
+      CONV_RUN(1)
+      CONV_RUN(2)
+      CONV_RUN(3)
+      CONV_RUN(4)
+      CONV_RUN(5)
+      CONV_RUN(6)
+      CONV_RUN(7)
+      CONV_RUN(8)
+    }
+#undef CONV_RUN
+  }
+  const int rpc = 1;
   const dim3 grid((T + rpc - 1) / rpc, (width + 255) / 256);
   if (f32)
     B200_CUDA(launch(canon_conv_kernel<float>, grid, dim3(256), (size_t)0, s, h, w, (float*)out, width, taps, positions, row_to_seq,

@@ -190,6 +190,46 @@ def test_rotation_cache_and_attention_with_a_sink_and_a_far_key(f32, heads, kv_h
 
 
 @pytest.mark.parametrize("f32", [1, 0])
+@pytest.mark.parametrize("taps", [1, 2, 4, 8, 9])
+def test_input_convolution_over_long_steps_with_many_sequences(f32, taps):
+    """Steps of a hundred rows and more take the kernel that slides a window of inputs along a run of rows: sequences of one, two and
+    many rows side by side, runs that start in the middle of a sequence, then a second step that continues every sequence from its
+    tail (slots shuffled, the unused slot dirty)."""
+    g = torch.Generator().manual_seed(taps)
+    width, hist = 70, taps - 1
+    lens = [[1, 2, 3, 70, 5, 130, 17], [40, 1, 64, 2, 1, 33, 16]]
+    n_seq = len(lens[0])
+    h = [U.bf16_exact(torch.randn(lens[0][i] + lens[1][i], width, generator=g)) for i in range(n_seq)]
+    w = U.bf16_exact(0.5 * torch.randn(width, taps, generator=g))
+    want = [x.double() + O.causal_conv(x.double(), w.double()) for x in h]
+    slot_f = hist * width + 4
+    slots = [5, 0, 3, 1, 6, 2, 7]
+    state = dev(torch.full((8, slot_f), 9.0))
+    adt = _adt(f32)
+    done = [0] * n_seq
+    for step in range(2):
+        rows, pos, rts, start = [], [], [], [0]
+        for i in range(n_seq):
+            n = lens[step][i]
+            rows.append(h[i][done[i]:done[i] + n])
+            pos += list(range(done[i], done[i] + n))
+            rts += [i] * n
+            start.append(start[-1] + n)
+        x = dev(torch.cat(rows))
+        T = x.shape[0]
+        out = torch.zeros(T, width, dtype=adt, device=DEV)
+        check(lib().b200_canon_conv(f32, x.data_ptr(), dev(w).data_ptr(), out.data_ptr(), T, width, taps, i32(pos).data_ptr(), i32(rts).data_ptr(),
+                                    i32(start).data_ptr(), i32(slots).data_ptr(), state.data_ptr() if hist else None, slot_f, None))
+        sync()
+        for i in range(n_seq):
+            n = lens[step][i]
+            got = out[start[i]:start[i + 1]].float().cpu().double()
+            assert torch.allclose(got, want[i][done[i]:done[i] + n], atol=1e-5 if f32 else 3e-2, rtol=0 if f32 else 1e-2), (step, i)
+            done[i] += n
+    assert float(state[4].min()) == 9.0 and float(state[4].max()) == 9.0
+
+
+@pytest.mark.parametrize("f32", [1, 0])
 @pytest.mark.parametrize("ff", [7, 64, 1000])
 def test_polynomial_of_unit_rms_powers(f32, ff):
     g = torch.Generator().manual_seed(ff)
