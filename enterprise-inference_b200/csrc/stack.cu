@@ -627,7 +627,8 @@ static int stack_enqueue_step_hyper(b200_ctx* c, const StepArgs& a, cudaStream_t
   // closes the sublayer before, opens one with coefficients hc / norm (w, b) / convolution cw (tail at tail_off) into `out`
   // every sequence brings one row (decode): the convolution runs behind the norm in the same launch
   static const int fuse_env = getenv("B200_STACK_FUSE_CANON") ? atoi(getenv("B200_STACK_FUSE_CANON")) : 1;
-  const bool conv_fused = conv && fuse_env && S == T && (m.canon_taps == 1 || M->state);
+  const bool one_row_each = (a.n_seqs > 0 && a.n_seqs == T) || a.row_to_seq == nullptr;   // known, not assumed
+  const bool conv_fused = conv && fuse_env && one_row_each && (m.canon_taps == 1 || M->state);
   auto open = [&](const float* hc, const float* w, const float* b, const float* cw, int64_t tail_off, void* out, float* tap) -> int {
     if (conv_fused) {
       const bool was_first = first;

@@ -294,17 +294,25 @@ rms_rows_kernel(const float* __restrict__ u, const int32_t* __restrict__ rows, c
   for (int c = threadIdx.x; c < width; c += 256) stx<AT>(out, dst + c, row[c] * a);
 }
 
-// two neighbours at an even index in one access
-__device__ __forceinline__ void ld2(const float* p, int64_t i, float& a, float& b) {
-  const float2 v = *reinterpret_cast<const float2*>(p + i);
-  a = v.x, b = v.y;
+// gated rows of bf16 whose ff is a multiple of 8: eight neighbours per thread and trip (16-byte accesses), fp32 arithmetic
+__global__ void __launch_bounds__(256)
+ff_act_gated8_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int64_t rows, int ff, int kind, float limit) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int chunks = ff >> 3;
+  const int64_t n = rows * chunks;
+  for (int64_t i = blockIdx.x * 256ll + threadIdx.x; i < n; i += gridDim.x * 256ll) {
+    const int64_t t = i / chunks;
+    const int f = (int)(i - t * chunks) << 3;
+    const uint4 g = *reinterpret_cast<const uint4*>(in + t * 2 * ff + f), u = *reinterpret_cast<const uint4*>(in + t * 2 * ff + ff + f);
+    uint4 o;
+    o.x = pack_bf16(gate_combine(bf16lo(g.x), bf16lo(u.x), kind, limit), gate_combine(bf16hi(g.x), bf16hi(u.x), kind, limit));
+    o.y = pack_bf16(gate_combine(bf16lo(g.y), bf16lo(u.y), kind, limit), gate_combine(bf16hi(g.y), bf16hi(u.y), kind, limit));
+    o.z = pack_bf16(gate_combine(bf16lo(g.z), bf16lo(u.z), kind, limit), gate_combine(bf16hi(g.z), bf16hi(u.z), kind, limit));
+    o.w = pack_bf16(gate_combine(bf16lo(g.w), bf16lo(u.w), kind, limit), gate_combine(bf16hi(g.w), bf16hi(u.w), kind, limit));
+    *reinterpret_cast<uint4*>(out + t * ff + f) = o;
+  }
 }
-__device__ __forceinline__ void ld2(const __nv_bfloat16* p, int64_t i, float& a, float& b) {
-  const uint32_t v = *reinterpret_cast<const uint32_t*>(p + i);
-  a = bf16lo(v), b = bf16hi(v);
-}
-__device__ __forceinline__ void st2(float* p, int64_t i, float a, float b) { *reinterpret_cast<float2*>(p + i) = make_float2(a, b); }
-__device__ __forceinline__ void st2(__nv_bfloat16* p, int64_t i, float a, float b) { *reinterpret_cast<uint32_t*>(p + i) = pack_bf16(a, b); }
 
 // gated: out[t][f] = act(in[t][f]) * in[t][ff + f] over rows of 2 ff; plain: out[t][f] = act(in[t][f]) (in place allowed)
 template <typename AT>
@@ -312,17 +320,6 @@ __global__ void __launch_bounds__(256)
 ff_act_kernel(const AT* __restrict__ in, AT* __restrict__ out, int64_t total, int ff, int gated, int kind, float limit) {
   pdl_wait();
   pdl_launch_dependents();
-  if (gated && ff % 2 == 0 && (reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) % 8 == 0) {   // two neighbours per thread and trip
-    const int64_t rows = total / ff, pairs = ff >> 1, n2 = rows * pairs;
-    for (int64_t i = blockIdx.x * 256ll + threadIdx.x; i < n2; i += gridDim.x * 256ll) {
-      const int64_t t = i / pairs, f = (i - t * pairs) * 2;
-      float g0, g1, u0, u1;
-      ld2(in, t * 2 * ff + f, g0, g1);
-      ld2(in, t * 2 * ff + ff + f, u0, u1);
-      st2(out, t * ff + f, gate_combine(g0, u0, kind, limit), gate_combine(g1, u1, kind, limit));
-    }
-    return;
-  }
   for (int64_t i = blockIdx.x * 256ll + threadIdx.x; i < total; i += gridDim.x * 256ll) {
     if (gated) {
       const int64_t t = i / ff, f = i % ff;
@@ -459,6 +456,11 @@ int ff_act(bool f32, const void* in, void* out, int T, int ff, bool gated, int k
   const int64_t total = (int64_t)T * ff;
   if (total == 0) return B200_OK;
   const int grid = (int)std::min<int64_t>((total + 255) / 256, 148 * 16);
+  if (!f32 && gated && ff % 8 == 0 && (reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) % 16 == 0) {
+    const int g8 = (int)std::min<int64_t>((total / 8 + 255) / 256, 148 * 16);
+    B200_CUDA(launch(ff_act_gated8_kernel, dim3(g8), dim3(256), (size_t)0, s, (const __nv_bfloat16*)in, (__nv_bfloat16*)out, (int64_t)T, ff, kind, limit));
+    return B200_OK;
+  }
   if (f32)
     B200_CUDA(launch(ff_act_kernel<float>, dim3(grid), dim3(256), (size_t)0, s, (const float*)in, (float*)out, total, ff, gated ? 1 : 0, kind, limit));
   else

@@ -244,6 +244,21 @@ def test_polynomial_of_unit_rms_powers(f32, ff):
 
 
 @pytest.mark.parametrize("f32", [1, 0])
+@pytest.mark.parametrize("ff", [7, 24, 1024])
+def test_clamped_gate_activation_rows(f32, ff):
+    g = torch.Generator().manual_seed(ff)
+    gu = U.bf16_exact(2.0 * torch.randn(11, 2 * ff, generator=g))
+    adt = _adt(f32)
+    out = torch.zeros(11, ff, dtype=adt, device=DEV)
+    check(lib().b200_ff_act_limit(f32, dev(gu, adt).data_ptr(), out.data_ptr(), 11, ff, 1, pkg("_abi").ACT_SWIGLU_CLAMP, 1.25, None))
+    sync()
+    a, b = gu[:, :ff].double().clamp(max=1.25), gu[:, ff:].double().clamp(-1.25, 1.25)
+    want = a * torch.sigmoid(1.702 * a) * (b + 1.0)
+    assert float((gu[:, :ff] > 1.25).sum()) > 0 and float((gu[:, ff:] < -1.25).sum()) > 0
+    assert torch.allclose(out.float().cpu().double(), want, atol=1e-5 if f32 else 2e-2, rtol=1e-5 if f32 else 1e-2)
+
+
+@pytest.mark.parametrize("f32", [1, 0])
 @pytest.mark.parametrize("T,width,experts,top,ff", [(5, 40, 6, 2, 24), (130, 64, 5, 5, 16), (70, 72, 9, 1, 40), (3, 33, 4, 3, 7)])
 def test_chosen_softmax_router_and_clamped_experts(f32, T, width, experts, top, ff):
     """Logits with the bias inside, the largest win, weights over the winners alone; experts whose gate is capped from above and whose
