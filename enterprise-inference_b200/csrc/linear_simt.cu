@@ -2,7 +2,8 @@
 // 32-bit serving mode, and of shapes the tcgen05 path cannot address.  Weights stay bf16 in memory (their values are
 // exact in fp32); activations are fp32 or bf16 on either side.  64 x 64 output tile per CTA, k in steps of 16 through
 // shared memory, a 4 x 4 micro-tile per thread; the k loop runs in order, so a row's sums do not depend on what else is
-// in the step.
+// in the step.  Every 16-wide k block is summed on its own and then added to the running total: the rounding error of a
+// sum over k terms grows with sqrt(16) + sqrt(k / 16) instead of sqrt(k).
 #include "common.cuh"
 
 namespace b200 {
@@ -42,6 +43,11 @@ linear_simt_kernel(const XT* __restrict__ x, int64_t ldx, const __nv_bfloat16* _
       ws[c][r] = (n0 + r < n_out && k0 + c < k) ? __bfloat162float(w[(int64_t)(n0 + r) * k + k0 + c]) : 0.f;
     }
     __syncthreads();
+    float part[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) part[i][j] = 0.f;
 #pragma unroll
     for (int c = 0; c < kBK; ++c) {
       float a[4], b[4];
@@ -52,8 +58,12 @@ linear_simt_kernel(const XT* __restrict__ x, int64_t ldx, const __nv_bfloat16* _
 #pragma unroll
       for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        for (int j = 0; j < 4; ++j) part[i][j] = fmaf(a[i], b[j], part[i][j]);
     }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] += part[i][j];
     __syncthreads();
   }
 #pragma unroll

@@ -637,3 +637,29 @@ def test_random_weights_of_the_benchmark_run(model_a):
     out = eng.generate([_prompt(cfg, 30, 1), _prompt(cfg, 4, 2)], max_tokens=6)
     assert [len(o) for o in out] == [6, 6] and all(0 <= t < cfg["vocab"] for o in out for t in o)
     r.close()
+
+
+def test_samplers_and_log_probabilities_read_the_steps_logits(model_a):
+    """Sampled requests go through the framework's samplers after the step: with top_k = 1 a request at temperature 0.9 emits the
+    greedy tokens; the log-probabilities of the emitted tokens are the oracle's log-softmax (the samplers read bf16 logits); a
+    plain greedy request in the same batch is untouched by its neighbours."""
+    cfg, w = model_a
+    E = pkg("engine")
+    r = R.make_runner(cfg, w, "float32", max_tokens=64, max_model_len=256, n_blocks=40)
+    eng = E.LLMEngine(r, max_num_batched_tokens=64, max_num_seqs=4, max_model_len=256)
+    p = _prompt(cfg, 19, 31)
+    greedy = eng.generate([p], max_tokens=10)[0]
+    reqs = [E.Request("s", list(p), max_tokens=10, ignore_eos=True, temperature=0.9, top_k=1, seed=5),
+            E.Request("l", list(p), max_tokens=10, ignore_eos=True, logprobs=2),
+            E.Request("g", list(p), max_tokens=10, ignore_eos=True)]
+    for q in reqs:
+        eng.add_request(q)
+    while eng.has_work():
+        eng.step()
+    assert reqs[0].output_ids == greedy and reqs[1].output_ids == greedy and reqs[2].output_ids == greedy
+    ids = list(p)
+    for tok, (lp, top) in zip(reqs[1].output_ids, reqs[1].logprob_data):
+        z = torch.log_softmax(O.forward(cfg, w, ids)[-1], -1)
+        assert abs(lp - float(z[tok])) < 0.05 and top[0][0] == int(z.argmax())
+        ids.append(tok)
+    r.close()
