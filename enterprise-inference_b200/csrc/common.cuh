@@ -116,6 +116,12 @@ __device__ __forceinline__ bool elect_one() {
       : "=r"(pred));
   return pred != 0;
 }
+// Asks the lines of [p, p + bytes) into L2, the CTA's threads sharing the lines.  For what does not depend on the launch
+// before (weights, step inputs, state of the step before) it runs ahead of pdl_wait, while that launch still computes.
+__device__ __forceinline__ void prefetch_l2_span(const void* p, size_t bytes) {
+  const char* c = static_cast<const char*>(p);
+  for (size_t o = (size_t)threadIdx.x * 128; o < bytes; o += (size_t)blockDim.x * 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(c + o));
+}
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
 
@@ -225,7 +231,8 @@ int linear_tc_grouped(const __nv_bfloat16* x, int64_t ldx, int N, int n_tiles, c
                       const int32_t* tile_expert, __nv_bfloat16* y, int64_t ldy, const int32_t* row_pair, const float* wts,
                       float* out, cudaStream_t s);
 int linear_tc_grouped_gate_up(const __nv_bfloat16* x, int64_t ldx, int N, int n_tiles, const __nv_bfloat16* w, int experts, int ff,
-                              int k, const int32_t* tile_expert, __nv_bfloat16* y, cudaStream_t s);
+                              int k, const int32_t* tile_expert, __nv_bfloat16* y, cudaStream_t s, int act = 0, float act_limit = 0.f);
+// act: b200_act_kind of the gate in the epilogue (0: silu; B200_ACT_SWIGLU_CLAMP with act_limit)
 int rmsnorm(const __nv_bfloat16* x, __nv_bfloat16* res, const __nv_bfloat16* w, __nv_bfloat16* y, int T,
             int hidden, float eps, cudaStream_t s);
 // fp32 residual stream (RMSNorm folded into the linears): embedding rows -> sres/ssq; stream rows -> normed bf16

@@ -48,10 +48,18 @@ delta_prep_kernel(const AT* __restrict__ fused, int64_t ld, const AT* __restrict
                   float* __restrict__ vn, float* __restrict__ beta, float* __restrict__ decay, int heads, int kv_heads, int dim, int vdim,
                   int taps, int off_b) {
   extern __shared__ float xs[];   // [C] convolved and activated channels
-  pdl_wait();
-  pdl_launch_dependents();
   const int64_t t = blockIdx.x;
   const int qk = kv_heads * dim, C = 2 * qk + heads * vdim;
+  if (gridDim.x <= 128) {   // short steps wait on latency: weights and the sequence's tail go to L2 while the launch before runs
+    if (blockIdx.y == 0) {
+      prefetch_l2_span(conv_w, (size_t)C * taps * 4);
+      if (tails) prefetch_l2_span(tails + (int64_t)seq_slots[row_to_seq ? row_to_seq[t] : (int)t] * slot_stride, (size_t)(taps - 1) * C * 4);
+    } else {
+      prefetch_l2_span(dt_bias, (size_t)heads * decay_dim * 4);
+    }
+  }
+  pdl_wait();
+  pdl_launch_dependents();
   if (blockIdx.y == 1) {   // the second CTA of a row: beta and the decays (nothing of the convolution enters them)
     const int hd = heads * decay_dim;   // decay_dim: dim (one decay per key channel) or 1 (one per head)
     for (int h = threadIdx.x; h < heads; h += kPrepThreads) beta[t * heads + h] = sigmoid_f(ldx<AT>(fused, t * ld + off_b + h));

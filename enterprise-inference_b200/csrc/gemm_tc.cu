@@ -188,6 +188,7 @@ struct TcParams {
   // gate rows m*64.. and the matching up rows, fetched as two 64-row boxes (the layout kSiluMul expects, made by TMA)
   int gu_ff;
   int act;   // kSiluMul: b200_act_kind of the gate (0: silu, rounded to bf16 before the product as the fixed stack does)
+  float act_limit;   // B200_ACT_SWIGLU_CLAMP: the clamp of gate and up value
   // kScatter: row t of the launch goes to grp_out[grp_pair[t]][n_out] (fp32, unrounded) times grp_wt[grp_pair[t]];
   // grp_pair[t] < 0 marks a padding row
   // (both null: the identity and weight 1, i.e. a plain fp32 output)
@@ -255,7 +256,8 @@ __device__ __forceinline__ void finalize4(const TcParams& p, int m_tile, int lan
     const float g0 = lo ? v[0] : x[2], g1 = lo ? v[1] : x[3];
     const float u0 = lo ? x[0] : v[2], u1 = lo ? x[1] : v[3];
     const int f = m_tile * 64 + (lane & 15) * 4 + (lo ? 0 : 2);                  // output feature
-    const float o0 = (p.act == 0 ? silu_to_bf16(g0) : act_apply(g0, p.act)) * u0, o1 = (p.act == 0 ? silu_to_bf16(g1) : act_apply(g1, p.act)) * u1;
+    const float o0 = p.act == 0 ? silu_to_bf16(g0) * u0 : gate_combine(g0, u0, p.act, p.act_limit);
+    const float o1 = p.act == 0 ? silu_to_bf16(g1) * u1 : gate_combine(g1, u1, p.act, p.act_limit);
     __nv_bfloat16* dst = p.y + (int64_t)tok * p.ldy + f;
     if ((p.ldy % 2 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 3) == 0)) {
       *reinterpret_cast<uint32_t*>(dst) = pack_bf16(o0, o1);
@@ -1145,7 +1147,7 @@ static int launch_grouped_silu(const CUtensorMap& mw, const CUtensorMap& mx, con
 }
 
 int linear_tc_grouped_gate_up(const __nv_bfloat16* x, int64_t ldx, int N, int n_tiles, const __nv_bfloat16* w, int experts, int ff,
-                              int k, const int32_t* tile_expert, __nv_bfloat16* y, cudaStream_t s) {
+                              int k, const int32_t* tile_expert, __nv_bfloat16* y, cudaStream_t s, int act, float act_limit) {
   B200_REQUIRE(ff > 0 && ff % (kBlockM / 2) == 0 && k > 0 && k % 8 == 0, B200_ERR_UNSUPPORTED,
                "linear_tc_grouped_gate_up: ff=%d must be a multiple of 64, k=%d of 8", ff, k);
   B200_REQUIRE(x && w && y && tile_expert && reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0 &&
@@ -1171,6 +1173,8 @@ int linear_tc_grouped_gate_up(const __nv_bfloat16* x, int64_t ldx, int N, int n_
   p.grp_tile = tile_expert;
   p.gu_ff = ff;
   p.tile_n = N;
+  p.act = act;
+  p.act_limit = act_limit;
   CUtensorMap mw, mx;
   int rc = get_map(w, (uint64_t)experts * 2 * ff, (uint64_t)k, (uint64_t)k, kBlockM / 2, &mw);
   if (rc) return rc;

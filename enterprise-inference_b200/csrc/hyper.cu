@@ -63,6 +63,8 @@ template <> __device__ __forceinline__ void stv<__nv_bfloat16, 4>(__nv_bfloat16*
   *reinterpret_cast<uint2*>(p + i) = make_uint2(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]));
 }
 
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
 // The input convolution of a step whose sequences bring ONE row each (decode steps), fused behind the norm: the taps before
 // the row's own come from the sequence's tail in its state slot, which is shifted by one place and takes the row.
 struct HyperConv {
@@ -85,13 +87,39 @@ hyper_step_kernel(float* X, int64_t sstride, int init, const AT* __restrict__ y,
   extern __shared__ __align__(16) float hy_row[];
   __shared__ float red[32];
   __shared__ float coef[2 * kMaxN + kMaxN * kMaxN + kMaxN];   // a | b | M of the closing sublayer, then the opening a
+  __shared__ float* cv_slot_tail;
+  __shared__ int cv_pos;
+  // Weights do not depend on the launch before: the coefficients are fetched, and the rows of weights the later phases
+  // read are asked into L2, while that launch still runs (programmatic dependent launch).
+  const int nt = blockDim.x;
+  for (int i = threadIdx.x; i < 2 * N + N * N; i += nt) coef[i] = hc ? hc[i] : 0.f;
+  if (threadIdx.x < N) coef[2 * N + N * N + threadIdx.x] = open_in ? open_in[threadIdx.x] : 1.0f;
+  if (gridDim.x <= 256) {   // short steps: every CTA is on an SM at once and waits on latency, not on bandwidth
+    for (int c = threadIdx.x * 32; c < width; c += nt * 32) {
+      if (hc) prefetch_l2(scale + c);
+      if (nw) prefetch_l2(nw + c);
+      if (nb) prefetch_l2(nb + c);
+    }
+    if (cv.w)
+      for (int c = threadIdx.x * 32; c < width * cv.taps; c += nt * 32) prefetch_l2(cv.w + c);
+  }
+  if (cv.w) {
+    // the row's sequence, slot and position are step inputs (copied in before the step's first launch): the chain of lookups
+    // and the tail's way into L2 also run ahead of the wait
+    const int sq = cv.row_to_seq ? cv.row_to_seq[blockIdx.x] : (int)blockIdx.x;
+    const int hist0 = cv.taps - 1;
+    const float* tl = hist0 ? cv.tails + (int64_t)cv.seq_slots[sq] * cv.slot_stride : nullptr;
+    if (threadIdx.x == 0) {
+      cv_slot_tail = const_cast<float*>(tl);
+      cv_pos = cv.positions[blockIdx.x];
+    }
+    if (tl)
+      for (int c = threadIdx.x * 32; c < width * hist0; c += nt * 32) prefetch_l2(tl + c);
+  }
   pdl_wait();
   pdl_launch_dependents();
   const int64_t t = blockIdx.x;
   const int64_t src = rows ? (int64_t)rows[t] : t;
-  const int nt = blockDim.x;
-  for (int i = threadIdx.x; i < 2 * N + N * N; i += nt) coef[i] = hc ? hc[i] : 0.f;
-  if (threadIdx.x < N) coef[2 * N + N * N + threadIdx.x] = open_in ? open_in[threadIdx.x] : 1.0f;
   __syncthreads();
   const float* cb = coef + N;
   const float* cm = coef + 2 * N;
@@ -183,9 +211,8 @@ hyper_step_kernel(float* X, int64_t sstride, int init, const AT* __restrict__ y,
     return;
   }
   // one row per sequence: out = h + sum_j w[:, j] in_j with in_(taps-1) = h and the earlier inputs from the tail
-  const int s = cv.row_to_seq ? cv.row_to_seq[t] : (int)t;
-  const int hist = cv.taps - 1, p0 = cv.positions[t];
-  float* tail = hist ? cv.tails + (int64_t)cv.seq_slots[s] * cv.slot_stride : nullptr;
+  const int hist = cv.taps - 1, p0 = cv_pos;
+  float* tail = cv_slot_tail;
   for (int c = threadIdx.x; c < width; c += nt) {
     const float h = (hy_row[c] - mean) * rstd * nw[c] + (nb ? nb[c] : 0.f);
     float old[kHyMaxTaps];

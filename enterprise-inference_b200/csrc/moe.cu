@@ -514,6 +514,10 @@ static int moe_experts_tc(const __nv_bfloat16* x, const __nv_bfloat16* w_gu, con
     if (rc) return rc;
     rc = ff_act(false, act, act, (int)rows, ff, false, form.act, s);
     if (rc) return rc;
+  } else if (form.act == B200_ACT_SWIGLU_CLAMP && fuse_env && ff % 64 == 0 && (N <= 64 || fuse_env > 1)) {
+    // the clamped gate in the same epilogue (it sees the bf16-rounded gate and up values the separate kernel would read)
+    rc = linear_tc_grouped_gate_up(xg, width, N, n_tiles, w_gu, experts, ff, width, tile_expert, act, s, form.act, form.limit);
+    if (rc) return rc;
   } else if (form.act != B200_ACT_SILU) {
     rc = linear_tc_grouped(xg, width, N, n_tiles, w_gu, experts, 2 * ff, width, tile_expert, gu, 2 * ff, nullptr, nullptr, nullptr, s);
     if (rc) return rc;

@@ -34,10 +34,15 @@ ssd_prep_kernel(const AT* __restrict__ fused, int64_t ld, const float* __restric
                 const int32_t* __restrict__ row_to_seq, const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slots,
                 const float* __restrict__ tails, int64_t slot_stride, float* __restrict__ xn, float* __restrict__ bn, float* __restrict__ cn,
                 float* __restrict__ dt, float* __restrict__ decay, int heads, int groups, int state, int vdim, int taps) {
-  pdl_wait();
-  pdl_launch_dependents();
   const int64_t t = blockIdx.x;
   const int inner = heads * vdim, gn = groups * state, C = inner + 2 * gn;
+  if (gridDim.x <= 128 && blockIdx.y == 0) {   // short steps wait on latency: weights and the tail go to L2 while the launch before runs
+    prefetch_l2_span(conv_w, (size_t)C * taps * 4);
+    if (conv_b) prefetch_l2_span(conv_b, (size_t)C * 4);
+    if (tails) prefetch_l2_span(tails + (int64_t)seq_slots[row_to_seq ? row_to_seq[t] : (int)t] * slot_stride, (size_t)(taps - 1) * C * 4);
+  }
+  pdl_wait();
+  pdl_launch_dependents();
   if (blockIdx.y == 1) {   // the second CTA of a row: step sizes and decays
     for (int h = threadIdx.x; h < heads; h += kSsdThreads) {
       const float d = softplus_f(ldx<AT>(fused, t * ld + inner + C + h) + dt_bias[h]);
@@ -68,6 +73,7 @@ __global__ void __launch_bounds__(kSsdThreads)
 ssd_gate_norm_kernel(const float* __restrict__ o, const float* __restrict__ xn, const float* __restrict__ skip, const AT* __restrict__ z,
                      int64_t ldz, const float* __restrict__ w, AT* __restrict__ out, int heads, int vdim, int norm_groups, float eps) {
   extern __shared__ float gy[];   // [inner] gated rows, then [norm_groups] scale factors
+  if (gridDim.x <= 128) prefetch_l2_span(w, (size_t)heads * vdim * 4);
   pdl_wait();
   pdl_launch_dependents();
   const int64_t t = blockIdx.x;

@@ -299,6 +299,38 @@ def test_chosen_softmax_router_and_clamped_experts(f32, T, width, experts, top, 
     assert torch.allclose(parts.cpu().double(), want, atol=2e-5 if f32 else 4e-2, rtol=1e-4 if f32 else 3e-2)
 
 
+def test_clamped_gate_in_the_grouped_linears_epilogue_agrees_with_the_separate_kernel():
+    """bf16 experts whose ff is a multiple of 64: steps with small token tiles clamp and multiply in the gate|up linear's epilogue,
+    steps with 128-row tiles run the activation kernel; the same six tokens get the same rows either way, and the oracle's."""
+    g = torch.Generator().manual_seed(77)
+    width, ff, experts, top, limit = 64, 128, 4, 2, 0.9
+    x = U.bf16_exact(torch.randn(600, width, generator=g))
+    wr = U.bf16_exact(torch.randn(experts, width, generator=g) * 3.0 * width ** -0.5)
+    bias = torch.randn(experts, generator=g)
+    wg = U.bf16_exact(torch.randn(experts, ff, width, generator=g) * 2.0 * width ** -0.5)
+    wu = U.bf16_exact(torch.randn(experts, ff, width, generator=g) * 2.0 * width ** -0.5)
+    wd = U.bf16_exact(torch.randn(experts, width, ff, generator=g) * ff ** -0.5)
+    gu = dev(torch.cat([torch.cat([wg[e], wu[e]]) for e in range(experts)]), torch.bfloat16)
+    dn = dev(wd.reshape(-1, ff), torch.bfloat16)
+    ids_w, wt_w = O.route(x.double(), wr.double(), bias.double(), top)
+    got = []
+    for T in (6, 600):
+        ids, wts = dev(ids_w[:T].int()), dev(wt_w[:T].float())
+        ws = dev(torch.zeros(lib().b200_moe_workspace_bytes(T, top, experts, width, ff) // 4 + 64, dtype=torch.int32))
+        parts = torch.zeros(T, top, width, device=DEV)
+        check(lib().b200_moe_experts_limit(0, dev(x[:T], torch.bfloat16).data_ptr(), gu.data_ptr(), dn.data_ptr(), ids.data_ptr(), wts.data_ptr(), T,
+                                           width, ff, experts, top, parts.data_ptr(), ws.data_ptr(), 1, pkg("_abi").ACT_SWIGLU_CLAMP, limit, None))
+        sync()
+        got.append(parts[:6].cpu().double())
+    want = torch.zeros(6, top, width, dtype=torch.float64)
+    for t in range(6):
+        for j in range(top):
+            e = int(ids_w[t, j])
+            want[t, j] = wt_w[t, j] * O.expert(x[t:t + 1].double(), wg[e].double(), wu[e].double(), wd[e].double(), limit)[0]
+    assert torch.allclose(got[0], got[1], atol=1e-6, rtol=1e-6)
+    assert torch.allclose(got[0], want, atol=4e-2, rtol=3e-2)
+
+
 @pytest.mark.parametrize("f32", [1, 0])
 @pytest.mark.parametrize("heads,kv_heads,dim,vdim,taps", [(4, 2, 20, 12, 3), (1, 1, 72, 40, 1), (3, 3, 33, 70, 5), (2, 1, 130, 8, 2)])
 def test_head_decay_delta_rule_in_portions_with_two_sequences_and_dirty_slots(f32, heads, kv_heads, dim, vdim, taps):
