@@ -317,7 +317,10 @@ int hyper_step_n(float* X, int64_t sstride, int init, const void* y, const float
                          reinterpret_cast<uintptr_t>(scale) | reinterpret_cast<uintptr_t>(nw) | reinterpret_cast<uintptr_t>(nb) |
                          reinterpret_cast<uintptr_t>(h_f32) | reinterpret_cast<uintptr_t>(h_act) | reinterpret_cast<uintptr_t>(sum_out);
   if (N <= 4 && width % 4 == 0 && sstride % 4 == 0 && ptrs % 16 == 0) {
-    const int threads = std::min(1024, std::max(128, (width / 4 + 31) / 32 * 32));
+    // short steps: one trip per thread (latency); long steps: CTAs of 128 threads, so that many share an SM and one's block sums
+    // hide behind the others' loads (2048 rows of width 2048, 4 streams: 45 us with 512 threads, 34 us with 128)
+    int threads = std::min(1024, std::max(128, (width / 4 + 31) / 32 * 32));
+    if (R >= 512) threads = 128;
     static bool done[64] = {};
     if (smem > 48 * 1024) B200_CUDA(ensure_dynamic_smem(hyper_step_kernel<AT, N, 4>, 200 * 1024, done));
     B200_CUDA(launch(hyper_step_kernel<AT, N, 4>, dim3(R), dim3(threads), smem, s, X, sstride, init, (const AT*)y, parts, n_parts, scale, hc, mult,
