@@ -150,8 +150,8 @@ parallel_close_kernel(float* __restrict__ u, const AT* __restrict__ y_mix, const
 // hc[t] = h[t] + sum_j w[:, j] * h[t - taps + 1 + j] along each sequence (zeros before position 0).  Rows whose window
 // stays inside the step's portion of the sequence are one CTA each.  The first row of a portion also serves the next
 // taps - 2 rows (those whose window reaches into the state slot's tail), then writes the new tail: every read of the old
-// tail happens in the one CTA that overwrites it.  Long steps give a CTA several consecutive rows (rows_per_cta): a row's
-// CTA starts with three dependent lookups (sequence, bounds, position), which one CTA per row pays once per row.
+// tail happens in the one CTA that overwrites it.  This form serves short steps and more than 8 taps (one row per CTA:
+// rows_per_cta is 1); steps of 64 rows and more with at most 8 taps take canon_conv_run_kernel below.
 constexpr int kMaxTaps = 16;
 template <typename AT>
 __global__ void __launch_bounds__(256)
